@@ -42,14 +42,16 @@ __global__ void embed_scaled_kernel(float* __restrict__ out, float* __restrict__
 
 // ------------------------------------------------------------------ router by scores
 // z[e] = x . w[e] (32-bit accumulation; x in X), or, with w == null, x[t, e] holds z already.
-// score_fn 0: s = sigmoid(z); 1: s = z.  The `top` largest s are chosen, by their z (the same
+// score_fn 0: s = sigmoid(z); 1: s = z; 2: s = softmax(z) over ALL experts.  Chosen scores are
+// multiplied by `factor`.  The `top` largest s are chosen, by their z (the same
 // order, and large logits whose sigmoids all round to 1 still differ; ties: the lower index).  weights[t, e] = s[e] at chosen experts (divided by the chosen scores' sum when
 // `renorm`), zero elsewhere; chosen / chosen_w list them by rank.
 template <typename X, typename W>
 __global__ void route_scores_kernel(float* __restrict__ weights, int* __restrict__ chosen,
                                     float* __restrict__ chosen_w, const X* __restrict__ x,
                                     long x_ld, const W* __restrict__ w, int n_tokens, int width,
-                                    int n_experts, int top, int score_fn, int renorm) {
+                                    int n_experts, int top, int score_fn, int renorm,
+                                    float factor) {
     extern __shared__ float s[];                 // [n_experts]
     prb_grid_launch_dependents();
     const int t = blockIdx.x;
@@ -74,6 +76,12 @@ __global__ void route_scores_kernel(float* __restrict__ weights, int* __restrict
     __syncthreads();
     if (threadIdx.x == 0) {
         float sum = 0.0f;
+        float z_max = -INFINITY, z_den = 1.0f;
+        if (score_fn == 2) {                    // the softmax's maximum and denominator, in index order
+            for (int e = 0; e < n_experts; ++e) z_max = fmaxf(z_max, s[e]);
+            z_den = 0.0f;
+            for (int e = 0; e < n_experts; ++e) z_den += expf(s[e] - z_max);
+        }
         for (int k = 0; k < top; ++k) {
             int arg = -1;
             float best = -INFINITY;
@@ -82,7 +90,8 @@ __global__ void route_scores_kernel(float* __restrict__ weights, int* __restrict
                 if (v == v && (arg < 0 || v > best)) { best = v; arg = e; }
             }
             if (arg < 0) arg = k;               // (a row of NaNs: padding, or a fault upstream)
-            const float score = score_fn == 0 ? sigmoidf_(best) : best;
+            const float score = score_fn == 0 ? sigmoidf_(best)
+                              : score_fn == 2 ? expf(best - z_max) / z_den : best;
             chosen[(size_t)t * top + k] = arg;
             chosen_w[(size_t)t * top + k] = score;
             sum += score;
@@ -91,6 +100,7 @@ __global__ void route_scores_kernel(float* __restrict__ weights, int* __restrict
         for (int k = 0; k < top; ++k) {
             float p = chosen_w[(size_t)t * top + k];
             if (renorm) p /= sum;
+            p *= factor;
             chosen_w[(size_t)t * top + k] = p;
             weights[(size_t)t * n_experts + chosen[(size_t)t * top + k]] = p;
         }
@@ -262,17 +272,17 @@ PRB_API int prb_embed_scaled(float* out, float* keep, const int* tokens, const v
 
 PRB_API int prb_route_scores(float* weights, int* chosen, float* chosen_w, const void* x, long x_ld,
                              const void* w, int n_tokens, int width, int n_experts, int top,
-                             int score_fn, int renorm, int x_dtype, int w_dtype,
+                             int score_fn, int renorm, float factor, int x_dtype, int w_dtype,
                              cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (width <= 0 || n_experts <= 0 || top <= 0 || top > n_experts || n_experts > 8192)
         return PRB_E_SIZE;
-    if (score_fn < 0 || score_fn > 1) return PRB_E_ARG;
+    if (score_fn < 0 || score_fn > 2) return PRB_E_ARG;
     const size_t smem = (size_t)n_experts * sizeof(float);
 #define ROUTE(XT, WT)                                                                          \
     route_scores_kernel<XT, WT><<<n_tokens, 128, smem, stream>>>(                              \
         weights, chosen, chosen_w, (const XT*)x, x_ld, (const WT*)w, n_tokens, width, n_experts, \
-        top, score_fn, renorm)
+        top, score_fn, renorm, factor)
     if (w == nullptr) w_dtype = PRB_F32;
     if (x_dtype == PRB_F32 && w_dtype == PRB_F32) ROUTE(float, float);
     else if (x_dtype == PRB_F32 && w_dtype == PRB_BF16) ROUTE(float, __nv_bfloat16);

@@ -93,8 +93,10 @@ class GatedMLP(FeedForward):
 
 class GatedMoE(FeedForward):
     """A router chooses ``top`` of ``experts`` gated feed-forwards per token (logits in
-    32-bit accumulators plus a bias; weights = softmax over the chosen logits alone); an
-    optional shared expert runs for every token.
+    32-bit accumulators plus a bias, if the router has one); an optional shared expert runs for
+    every token.  ``score`` says what the weights are: "softmax_chosen" (the default), the
+    softmax over the chosen logits alone; "softmax", the chosen experts' shares of the softmax
+    over ALL experts (``renormalize``: divided by their sum), times ``router_scale``.
 
     All experts' gate and up rows, the shared expert's, the router's and whatever an
     arrangement fuses in are ONE matrix product; the activations of experts a token did not
@@ -111,6 +113,13 @@ class GatedMoE(FeedForward):
         self.shared_inner = int(p.get("shared_inner") or 0)
         self.limit, self.shared_limit = float(p["limit"]), float(p.get("shared_limit") or 0.0)
         self.act_alpha, self.up_shift = float(p["act_alpha"]), float(p["up_shift"])
+        self.score = p.get("score", "softmax_chosen")
+        self.renormalize = bool(p.get("renormalize", False))
+        self.router_scale = float(p.get("router_scale", 1.0))
+        if self.score not in ("softmax_chosen", "softmax"):
+            raise ValueError(f"gated_moe: unknown score {self.score!r}")
+        if not 1 <= self.top <= n:
+            raise ValueError(f"gated_moe: top {self.top} of {n} experts")
         self.runtime = runtime
         pre = p["prefix"]
 
@@ -129,7 +138,10 @@ class GatedMoE(FeedForward):
             self.input.add("shared_up", need("shared.up", (self.shared_inner, width)))
             downs.append(need("shared.down", (width, self.shared_inner)))
         self.input.add("router", need("router", (n, width)))
-        self.router_bias = need("router.b", (n,)).to(torch.float32).contiguous()
+        self.router_bias = need("router.b", (n,)).to(torch.float32).contiguous() \
+            if p.get("router_bias", True) else None
+        if self.score == "softmax" and self.router_bias is not None:
+            raise ValueError("gated_moe: the softmax over all experts takes no router bias")
         self.down = padded_linear(torch.cat(downs, dim=1), runtime)
 
     def fuse_input_rows(self, name: str, weight) -> str:
@@ -146,8 +158,13 @@ class GatedMoE(FeedForward):
         scale = ctx.scratch("moe_scale", (cap, self.experts), torch.float32)[:t]
         chosen = ctx.scratch("moe_chosen", (cap, self.top), torch.int32)[:t]
         chosen_w = ctx.scratch("moe_chosen_w", (cap, self.top), torch.float32)[:t]
-        ops.route(scale, chosen, chosen_w, self.input.view(proj, "router"), None, self.router_bias,
-                  self.top)
+        if self.score == "softmax":
+            ops.route_scores(scale, chosen, chosen_w, self.input.view(proj, "router"), None,
+                             self.top, score="softmax", renormalize=self.renormalize,
+                             factor=self.router_scale)
+        else:
+            ops.route(scale, chosen, chosen_w, self.input.view(proj, "router"), None,
+                      self.router_bias, self.top)
         n_act = self.experts * self.inner
         a = ctx.scratch_zero("moe_act", (cap, self.down.n_in), self.runtime.dtype)[:t]
         ops.gated_pair(a, proj, cols["gate"][0], cols["up"][0], n_act, limit=self.limit,

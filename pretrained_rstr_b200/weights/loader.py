@@ -45,6 +45,7 @@ class TensorExpectation:
     shape: Tuple[int, ...]
     kind: str = "float"          # "float" or "int"
     optional: bool = False       # may be absent from the file (the part then does without it)
+    free_dims: Tuple[int, ...] = ()   # dimensions whose size the file decides (a low rank, say)
 
 
 def _stored_dtype(dtype: torch.dtype, kind: str) -> torch.dtype:
@@ -127,7 +128,8 @@ def load_weights(folder: str, expected: Dict[str, TensorExpectation], device,
         exp = expected[name]
         shape = f.shape(stored_name)
         dtype = f.dtype(stored_name)
-        if tuple(shape) != tuple(exp.shape):
+        if len(shape) != len(exp.shape) or any(
+                a != b for i, (a, b) in enumerate(zip(shape, exp.shape)) if i not in exp.free_dims):
             wrong.append(f"{stored_name}: expected {list(exp.shape)}, found {list(shape)}")
         elif exp.kind == "float" and not dtype.is_floating_point:
             wrong.append(f"{stored_name}: expected a floating-point tensor, found {dtype}")
