@@ -147,7 +147,7 @@ def _declare(h: ctypes.CDLL) -> None:
     h.prb_latent_attention.argtypes = [P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, I, I, P, P]
     h.prb_latent_unfold.argtypes = [P, L, P, P, P, L, I, I, I, I, I, I, P]
     h.prb_embed_scaled.argtypes = [P, P, P, P, I, I, I, F, I, P, P]
-    h.prb_route_scores.argtypes = [P, P, P, P, L, P, I, I, I, I, I, I, I, I, P]
+    h.prb_route_scores.argtypes = [P, P, P, P, L, P, I, I, I, I, I, I, F, I, I, P]
     h.prb_routed_act.argtypes = [P, L, P, L, I, I, I, P, L, I, I, I, I, P]
     h.prb_retention_lanes.argtypes = [I]
     h.prb_retention_scan.argtypes = [P, P, L, I, I, I, P, P, P, P, P, P, I, I, I, I, I, I, I, F, I,
@@ -177,6 +177,21 @@ def _declare(h: ctypes.CDLL) -> None:
     h.prb_retention_step.argtypes = [P, L, P, L, I, I, I, I, P, P, P, P, P, P, I, I, I, I, I, I, I,
                                      F, F, I, P, P]
     h.prb_retention_step.restype = c_int
+    h.prb_tmix_lanes.argtypes = [I]
+    h.prb_tmix_shift.argtypes = [P, L, P, L, P, P, P, P, P, P, I, I, I, I, I, P, P]
+    h.prb_tmix_scan.argtypes = [P, L, P, L, I, I, I, I, P, P, P, P, P, L, P, P, P, P, I, I, I, I,
+                                I, I, I, I, P, P]
+    h.prb_tmix_finish.argtypes = [P, L, P, L, P, L, I, P, P, I, I, I, F, F, I, P]
+    h.prb_wattn_prepare.argtypes = [P, P, P, L, I, I, I, P, P, P, P, P, I, I, I, I, I, I, F, F, I,
+                                    I, I, I, P, P]
+    h.prb_wattn.argtypes = [P, L, P, P, P, P, P, P, L, P, I, I, I, I, I, I, I, I, I, I, F, F, I, I,
+                            P, P]
+    h.prb_wattn_tile_rows.argtypes = [I, I, I, I]
+    h.prb_wattn_tile.argtypes = [P, L, P, P, P, P, P, P, L, P, I, I, I, I, I, I, I, I, I, I, I, F,
+                                 F, I, I, P, P]
+    for name in ("prb_tmix_lanes", "prb_tmix_shift", "prb_tmix_scan", "prb_tmix_finish",
+                 "prb_wattn_prepare", "prb_wattn", "prb_wattn_tile_rows", "prb_wattn_tile"):
+        getattr(h, name).restype = c_int
     for name in ("prb_embed_scaled", "prb_route_scores", "prb_routed_act", "prb_retention_lanes",
                  "prb_retention_scan", "prb_retention_finish", "prb_diff_prepare",
                  "prb_diff_attention"):
@@ -1156,16 +1171,17 @@ def embed_scaled(out, tokens, table, scale: float, keep=None, status=None) -> No
                                   _p(status), _stream()), what)
 
 
-SCORE_CODES = {"sigmoid": 0, "identity": 1}
+SCORE_CODES = {"sigmoid": 0, "identity": 1, "softmax": 2}
 ROUTED_ACT_CODES = {"relu_squared": 0, "relu": 1, "gelu_new": 2, "silu": 3}
 
 
 def route_scores(weights, chosen, chosen_w, x, w, top: int, score: str = "sigmoid",
-                 renormalize: bool = False) -> None:
+                 renormalize: bool = False, factor: float = 1.0) -> None:
     """Router by independent scores: z = x . w^T in 32-bit (x [T, width] float32 or bfloat16; w
     [experts, width]), or, with ``w`` None, x [T, experts] holds z already (possibly a column
-    slice of a wider tensor); s = sigmoid(z) or z; the ``top`` largest; weights float32 [T,
-    experts] hold the chosen scores (divided by their sum if ``renormalize``) and zero
+    slice of a wider tensor); s = sigmoid(z), z, or softmax(z) over all experts; the ``top``
+    largest; weights float32 [T, experts] hold the chosen scores (divided by their sum if
+    ``renormalize``, then times ``factor``) and zero
     elsewhere; chosen int32 [T, top] and chosen_w float32 [T, top] list them by rank."""
     what = "route_scores"
     if not x.is_cuda or x.stride(1) != 1:
@@ -1183,7 +1199,7 @@ def route_scores(weights, chosen, chosen_w, x, w, top: int, score: str = "sigmoi
         raise KernelArgumentError(f"{what}: shapes do not fit")
     _check(lib().prb_route_scores(_p(weights), _p(chosen), _p(chosen_w), _p(x), x.stride(0), _p(w),
                                   n, width, experts, int(top), SCORE_CODES[score],
-                                  1 if renormalize else 0, dtype_code(x.dtype),
+                                  1 if renormalize else 0, float(factor), dtype_code(x.dtype),
                                   F32 if w is None else dtype_code(w.dtype), _stream()), what)
 
 
@@ -1432,3 +1448,169 @@ def diff_attention(out, q, cache, block_table, seq_of_token, positions, heads: i
                                     float(scale), float(lam), float(eps), float(out_scale),
                                     dtype_code(cache.dtype), dtype_code(out.dtype), _p(status),
                                     _stream()), what)
+
+
+# ------------------------------------------------------------------------- time mixing
+def tmix_lanes(dim: int) -> int:
+    """Lanes a column of the time-mixing state is spread over (0: the head size is beyond the
+    scan kernel)."""
+    return int(lib().prb_tmix_lanes(int(dim)))
+
+
+def tmix_shift(out, h, prev_state, mu, seq_of_token, positions, q_start, state_slot,
+               status=None) -> None:
+    """The blends of a token's input with the previous token's: out[t, s * width + i] =
+    h[t, i] + (h[t - 1, i] - h[t, i]) * mu[s, i] for each of mu's rows s.  The row before a
+    request's first token of the step is the request's row of ``prev_state`` [slots, width]
+    (zeros at position 0)."""
+    what = "tmix_shift"
+    _need(mu, torch.float32, "mu", what)
+    for name, t in (("seq_of_token", seq_of_token), ("positions", positions),
+                    ("q_start", q_start), ("state_slot", state_slot)):
+        _need(t, torch.int32, name, what)
+    n, width = h.shape
+    n_mix = mu.shape[0]
+    if not h.is_cuda or h.stride(1) != 1 or out.dtype != h.dtype or prev_state.dtype != h.dtype or \
+            out.stride(1) != 1 or out.shape[0] < n or out.shape[1] < n_mix * width or \
+            mu.shape[1] != width or prev_state.shape[1] != width or not prev_state.is_contiguous():
+        raise KernelArgumentError(f"{what}: shapes or types do not fit")
+    _check(lib().prb_tmix_shift(_p(out), out.stride(0), _p(h), h.stride(0), _p(prev_state), _p(mu),
+                                _p(seq_of_token), _p(positions), _p(q_start), _p(state_slot), n,
+                                width, n_mix, prev_state.shape[0], dtype_code(h.dtype), _p(status),
+                                _stream()), what)
+
+
+def tmix_scan(raw, proj, r_col: int, k_col: int, v_col: int, lr_col: int, w2, w0, u, state, h,
+              prev_state, q_start, state_slot, positions, n_requests: int, heads: int, dim: int,
+              vdim: int, status=None) -> None:
+    """The recurrence over the step's tokens, request by request: per head o_t = (S + diag(u)
+    k_t v_t^T)^T r_t, then S <- diag(w_t) S + k_t v_t^T with w_t = exp(-exp(w0 + w2 tanh(lr_t)));
+    r, k, v and lr are column ranges of ``proj`` (float32).  ``state`` [slots, heads, vdim, dim]
+    float32 is read (zero at position 0) and written back; ``prev_state`` [slots, width]
+    receives the request's last row of ``h``.  raw float32 [T, heads * vdim]."""
+    what = "tmix_scan"
+    for name, t in (("raw", raw), ("w2", w2), ("w0", w0), ("u", u), ("state", state)):
+        _need(t, torch.float32, name, what)
+    for name, t in (("q_start", q_start), ("state_slot", state_slot), ("positions", positions)):
+        _need(t, torch.int32, name, what)
+    if not proj.is_cuda or proj.dtype != torch.float32 or proj.stride(1) != 1:
+        raise KernelArgumentError(f"{what}: proj must be float32 on CUDA with unit inner stride")
+    rank = w2.shape[1]
+    width = h.shape[1]
+    if tuple(state.shape[1:]) != (heads, vdim, dim) or w2.shape[0] != heads * dim or \
+            w0.numel() != heads * dim or u.numel() != heads * dim or \
+            max(r_col, k_col) + heads * dim > proj.shape[1] or v_col + heads * vdim > proj.shape[1] \
+            or lr_col + rank > proj.shape[1] or raw.shape[1] < heads * vdim or \
+            prev_state.dtype != h.dtype or prev_state.shape != (state.shape[0], width) or \
+            h.stride(1) != 1 or q_start.numel() < n_requests + 1:
+        raise KernelArgumentError(f"{what}: shapes or types do not fit")
+    _check(lib().prb_tmix_scan(_p(raw), raw.stride(0), _p(proj), proj.stride(0), int(r_col),
+                               int(k_col), int(v_col), int(lr_col), _p(w2), _p(w0), _p(u), _p(state),
+                               _p(h), h.stride(0), _p(prev_state), _p(q_start), _p(state_slot),
+                               _p(positions), int(n_requests), heads, dim, vdim, rank, width,
+                               state.shape[0], dtype_code(h.dtype), _p(status), _stream()), what)
+
+
+def tmix_finish(out, raw, proj, g_col: int, norm_w, seq_of_token, heads: int, vdim: int,
+                eps: float, out_scale: float = 1.0) -> None:
+    """out[t, h] = raw[t, h] / sqrt(mean(raw[t, h]^2) + eps) * norm_w[h] * silu(proj[t, g_col +
+    h * vdim ...]) * out_scale per head; out in the activation type (rows may be wider)."""
+    what = "tmix_finish"
+    _need(raw, torch.float32, "raw", what)
+    _need(norm_w, torch.float32, "norm_w", what)
+    _need(seq_of_token, torch.int32, "seq_of_token", what)
+    n = raw.shape[0]
+    if not out.is_cuda or out.stride(1) != 1 or out.shape[0] < n or out.shape[1] < heads * vdim or \
+            proj.dtype != torch.float32 or proj.stride(1) != 1 or proj.shape[0] < n or \
+            g_col + heads * vdim > proj.shape[1] or norm_w.numel() != heads * vdim:
+        raise KernelArgumentError(f"{what}: shapes or types do not fit")
+    _check(lib().prb_tmix_finish(_p(out), out.stride(0), _p(raw), raw.stride(0), _p(proj),
+                                 proj.stride(0), int(g_col), _p(norm_w), _p(seq_of_token), n, heads,
+                                 vdim, float(eps), float(out_scale), dtype_code(out.dtype),
+                                 _stream()), what)
+
+
+# ------------------------------------------------------------------ windowed attention
+def wattn_prepare(q_out, cache, proj, q_col: int, k_col: int, v_col: int, q_norm, k_norm, slots,
+                  positions, freq, heads: int, kv_heads: int, dim: int, vdim: int, rot_dims: int,
+                  eps: float, temp_coef: float, temp_every: int, status=None) -> None:
+    """Queries and keys of the step's tokens as the attention reads them: a root-mean-square
+    norm over the whole projection (``q_norm`` / ``k_norm``: float32 weights, or None), the
+    query's temperature 1 + temp_coef * ln(floor((p + 1) / temp_every) + 1) (``temp_every`` 0:
+    none), the rotation of each head's first ``rot_dims`` coordinates (rotate-half).  Queries go
+    to q_out float32 [T, heads * dim]; keys and values to the tokens' cache rows [k | v]
+    (cache [pages, kv_heads, page size, dim + vdim]; ``slots`` None: nothing is cached)."""
+    what = "wattn_prepare"
+    _need(q_out, torch.float32, "q_out", what)
+    _need(cache, None, "cache", what)
+    _need(positions, torch.int32, "positions", what)
+    _need(freq, torch.float32, "freq", what)
+    if not proj.is_cuda or proj.dtype != torch.float32 or proj.stride(1) != 1:
+        raise KernelArgumentError(f"{what}: proj must be float32 on CUDA with unit inner stride")
+    n = q_out.shape[0]
+    pages, kvh, page_size, rowlen = cache.shape
+    if kvh != kv_heads or rowlen != dim + vdim or q_out.shape[1] != heads * dim or \
+            proj.shape[0] < n or q_col + heads * dim > proj.shape[1] or \
+            freq.numel() < max(1, rot_dims // 2):
+        raise KernelArgumentError(f"{what}: shapes do not fit")
+    if slots is not None:
+        _need(slots, torch.int32, "slots", what)
+        if k_col + kv_heads * dim > proj.shape[1] or v_col + kv_heads * vdim > proj.shape[1]:
+            raise KernelArgumentError(f"{what}: key or value columns outside the projection")
+    for name, t, size in (("q_norm", q_norm, heads * dim), ("k_norm", k_norm, kv_heads * dim)):
+        if t is not None:
+            _need(t, torch.float32, name, what)
+            if t.numel() != size:
+                raise KernelArgumentError(f"{what}: {name} must hold {size} numbers")
+    _check(lib().prb_wattn_prepare(_p(q_out), _p(cache), _p(proj), proj.stride(0), int(q_col),
+                                   int(k_col), int(v_col), _p(q_norm), _p(k_norm), _p(slots),
+                                   _p(positions), _p(freq), n, heads, kv_heads, dim, vdim,
+                                   int(rot_dims), float(eps), float(temp_coef), int(temp_every),
+                                   page_size, pages, dtype_code(cache.dtype), _p(status),
+                                   _stream()), what)
+
+
+def wattn_tile_rows(heads: int, kv_heads: int, dim: int, vdim: int) -> int:
+    """Most token rows a CTA of the tiled kernel takes; 0: sizes only the kernel of a CTA per
+    (token, head) takes."""
+    return int(lib().prb_wattn_tile_rows(heads, kv_heads, dim, vdim))
+
+
+def wattn(out, q, cache, block_table, seq_of_token, positions, heads: int, dim: int, vdim: int,
+          window: int, keep_first: int, scale: float, gate=None, slopes=None,
+          out_scale: float = 1.0, status=None, tile_rows: int = 0) -> None:
+    """Softmax attention over cache rows [k | v]: a query at position i sees key j <= i with
+    i - j < window (``window`` 0: all) or j < keep_first; score (q . k) * scale - slopes[h] * (i
+    - j); head h's result times sigmoid(gate[t, h]) (``gate``: float32, may be a column slice)
+    times ``out_scale``.  32-bit arithmetic; out in the cache's type.  ``tile_rows`` > 0: the
+    tiled kernel (a CTA per that many consecutive token rows and key/value head)."""
+    what = "wattn"
+    _need(q, torch.float32, "q", what)
+    _need(cache, None, "cache", what)
+    _need(block_table, torch.int32, "block_table", what)
+    _need(seq_of_token, torch.int32, "seq_of_token", what)
+    _need(positions, torch.int32, "positions", what)
+    n = q.shape[0]
+    pages, kv_heads, page_size, rowlen = cache.shape
+    if rowlen != dim + vdim or q.shape[1] != heads * dim or out.dtype != cache.dtype or \
+            out.stride(1) != 1 or out.shape[0] < n or out.shape[1] < heads * vdim:
+        raise KernelArgumentError(f"{what}: shapes or types do not fit")
+    gate_ld = 0
+    if gate is not None:
+        if gate.dtype != torch.float32 or gate.stride(1) != 1 or gate.shape[0] < n or \
+                gate.shape[1] < heads:
+            raise KernelArgumentError(f"{what}: gate must be float32 [rows, heads]")
+        gate_ld = gate.stride(0)
+    if slopes is not None:
+        _need(slopes, torch.float32, "slopes", what)
+        if slopes.numel() != heads:
+            raise KernelArgumentError(f"{what}: one slope per head")
+    common = (_p(out), out.stride(0), _p(q), _p(cache), _p(block_table), _p(seq_of_token),
+              _p(positions), _p(gate), gate_ld, _p(slopes), n, heads, kv_heads, dim, vdim,
+              page_size, block_table.shape[1], pages, int(window or 0), int(keep_first or 0))
+    tail = (float(scale), float(out_scale), dtype_code(cache.dtype), dtype_code(out.dtype),
+            _p(status), _stream())
+    if tile_rows > 0:
+        _check(lib().prb_wattn_tile(*common, int(tile_rows), *tail), what)
+    else:
+        _check(lib().prb_wattn(*common, *tail), what)

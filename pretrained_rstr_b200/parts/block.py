@@ -132,5 +132,36 @@ class PostNormGatedBlock(Block):
         ctx.stream_copy_by = self
 
 
+class ParallelBlock(Block):
+    """x <- x + (mixer(norm_1(x)) + feed_forward(norm_2(x))): both branches read the stream as
+    it was before the layer, each through a norm of its own, and their results join it in
+    32-bit.  Both norms run before either branch adds to the stream.  A layer without a
+    feed-forward has the mixer's norm alone."""
+    graph_safe = True
+
+    def __init__(self, mixer: Mixer, feed_forward: FeedForward, norms: Dict[str, Norm],
+                 width: int, runtime):
+        self.has_ff = not getattr(feed_forward, "is_none", False)
+        wanted = {"mixer", "feed_forward"} if self.has_ff else {"mixer"}
+        if set(norms) != wanted:
+            raise ValueError(f"parallel wants the norms {sorted(wanted)}, got {sorted(norms)}")
+        self.mixer, self.feed_forward = mixer, feed_forward
+        self.norms = dict(norms)
+        self.width, self.runtime = width, runtime
+
+    def forward(self, ctx, x, cache: LayerCache) -> None:
+        t = x.shape[0]
+        cap = ctx.token_capacity
+        h1 = ctx.scratch("block_normed", (cap, self.width), self.runtime.dtype)[:t]
+        self.norms["mixer"].forward(ctx, x, h1)
+        if self.has_ff:
+            h2 = ctx.scratch("block_normed_2", (cap, self.width), self.runtime.dtype)[:t]
+            self.norms["feed_forward"].forward(ctx, x, h2)
+        self.mixer.forward(ctx, h1, x, cache)
+        if self.has_ff:
+            self.feed_forward.forward(ctx, h2, x)
+
+
 register_part("arrangement", "pre_norm", PreNormBlock)
 register_part("arrangement", "post_norm_gated", PostNormGatedBlock)
+register_part("arrangement", "parallel", ParallelBlock)
