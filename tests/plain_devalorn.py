@@ -157,21 +157,30 @@ def shifted_blend(h: torch.Tensor, mu: torch.Tensor, before=None) -> torch.Tenso
     return h + (prev - h) * mu.to(h.dtype)
 
 
-def decayed_outer_states(r, k, v, w, u, state=None):
+def decayed_outer_states(r, k, v, w, u, state=None, cancelled: Optional[list] = None):
     """r, k, w [T, H, d]; v [T, H, dv]; u [H, d].  Per head, S [d, dv] from zero (or ``state``):
     o_t = (S + diag(u) k_t v_t^T)^T r_t, then S <- diag(w_t) S + k_t v_t^T.  Returns (o [T, H,
-    dv], last S [H, d, dv])."""
+    dv], last S [H, d, dv]).  ``cancelled`` receives, per token, the smallest ratio over the heads
+    of |o_t| to the same sum of absolute terms: near zero, o_t is what large terms leave of one
+    another, and its direction (all that a unit norm keeps) hangs on their last bits."""
     t, heads, d = r.shape
     S = torch.zeros(heads, d, v.shape[-1], dtype=r.dtype) if state is None else state.clone()
-    out = []
+    out, ratios = [], []
     for i in range(t):
         kv = k[i][:, :, None] * v[i][:, None, :]
-        out.append(torch.einsum("hkv,hk->hv", S + u[:, :, None] * kv, r[i]))
+        M = S + u[:, :, None] * kv
+        out.append(torch.einsum("hkv,hk->hv", M, r[i]))
+        if cancelled is not None:
+            bound = torch.einsum("hkv,hk->hv", M.abs(), r[i].abs())
+            ratios.append((out[-1].norm(dim=-1) / bound.norm(dim=-1).clamp_min(1e-300)).min())
         S = w[i][:, :, None] * S + kv
+    if cancelled is not None:
+        cancelled.append(torch.stack(ratios))
     return torch.stack(out), S
 
 
-def time_mix(h, tensors, prefix: str, mx: dict, eps: float, carried=None):
+def time_mix(h, tensors, prefix: str, mx: dict, eps: float, carried=None,
+             cancelled: Optional[list] = None):
     """The right mixer of a parallel layer.  ``carried``: (last input row, state) of the tokens
     before; returns (result, (last input row, state))."""
     dt = h.dtype
@@ -186,7 +195,7 @@ def time_mix(h, tensors, prefix: str, mx: dict, eps: float, carried=None):
     z = blend["g"] @ W("g").T
     gate = z * torch.sigmoid(z)
     w = torch.exp(-torch.exp(torch.tanh(blend["w"] @ W("w1").T) @ W("w2").T + W("w0"))).reshape(t, H, d)
-    o, state = decayed_outer_states(r, k, v, w, W("u"), state)
+    o, state = decayed_outer_states(r, k, v, w, W("u"), state, cancelled)
     o = unit_rms(o, eps).reshape(t, H * d) * W("norm") * gate
     return o @ W("o").T, (h[-1].clone(), state)
 
@@ -226,9 +235,11 @@ def softmax_routed_experts(h, tensors, prefix: str, mlp: dict, margins: Optional
 
 # --------------------------------------------------------------------------------- model
 def forward(tokens: List[int], tensors, cfg: dict, dtype=torch.float64, taps: Optional[list] = None,
-            margins: Optional[list] = None) -> torch.Tensor:
+            margins: Optional[list] = None, cancelled: Optional[list] = None) -> torch.Tensor:
     """Logits [T, vocab] of a whole sequence.  ``taps`` receives the stream after every layer;
-    ``margins`` per routed layer the router's closest call per token."""
+    ``margins`` per routed layer the router's closest call per token; ``cancelled`` per time
+    mixing how little of its terms each token's result keeps
+    (:func:`decayed_outer_states`)."""
     eps = float(cfg["norm"]["eps"])
     x = tensors["embed"].to(dtype)[torch.tensor(tokens)]
     kept = {}
@@ -238,7 +249,7 @@ def forward(tokens: List[int], tensors, cfg: dict, dtype=torch.float64, taps: Op
         h = weighted_norm(x, tensors[p + "norm1"], eps)
         if layer["type"] == "parallel":
             left, _ = gated_window_attention(h, tensors, p + "mix.left.", mx["left"])
-            right, _ = time_mix(h, tensors, p + "mix.right.", mx["right"], eps)
+            right, _ = time_mix(h, tensors, p + "mix.right.", mx["right"], eps, cancelled=cancelled)
             y = float(mx["left_scale"]) * left + float(mx["right_scale"]) * right
         else:
             src = mx.get("kv_from")
