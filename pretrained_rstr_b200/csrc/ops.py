@@ -180,17 +180,27 @@ def _declare(h: ctypes.CDLL) -> None:
     h.prb_tmix_lanes.argtypes = [I]
     h.prb_tmix_shift.argtypes = [P, L, P, L, P, P, P, P, P, P, I, I, I, I, I, P, P]
     h.prb_tmix_scan.argtypes = [P, L, P, L, I, I, I, I, P, P, P, P, P, L, P, P, P, P, I, I, I, I,
-                                I, I, I, I, P, P]
+                                I, I, I, I, P, P, L, I, P, F, F, P]
+    h.prb_tmix_step_supports.argtypes = [I, I]
+    h.prb_tmix_segment.argtypes = []
+    h.prb_tmix_max_segments.argtypes = [I, I]
+    h.prb_tmix_scan_segments.argtypes = [P, L, P, L, I, I, I, I, I, P, P, P, P, P, L, P, P, P, P,
+                                         I, I, I, I, I, I, I, I, I, P, P, P, I, P, P]
     h.prb_tmix_finish.argtypes = [P, L, P, L, P, L, I, P, P, I, I, I, F, F, I, P]
     h.prb_wattn_prepare.argtypes = [P, P, P, L, I, I, I, P, P, P, P, P, I, I, I, I, I, I, F, F, I,
                                     I, I, I, P, P]
     h.prb_wattn.argtypes = [P, L, P, P, P, P, P, P, L, P, I, I, I, I, I, I, I, I, I, I, F, F, I, I,
                             P, P]
     h.prb_wattn_tile_rows.argtypes = [I, I, I, I]
+    h.prb_wattn_single_supports.argtypes = [I, I, I, I]
+    h.prb_wattn_single.argtypes = list(h.prb_wattn.argtypes)
     h.prb_wattn_tile.argtypes = [P, L, P, P, P, P, P, P, L, P, I, I, I, I, I, I, I, I, I, I, I, F,
                                  F, I, I, P, P]
     for name in ("prb_tmix_lanes", "prb_tmix_shift", "prb_tmix_scan", "prb_tmix_finish",
-                 "prb_wattn_prepare", "prb_wattn", "prb_wattn_tile_rows", "prb_wattn_tile"):
+                 "prb_tmix_step_supports", "prb_tmix_segment", "prb_tmix_max_segments",
+                 "prb_tmix_scan_segments",
+                 "prb_wattn_prepare", "prb_wattn", "prb_wattn_tile_rows", "prb_wattn_tile",
+                 "prb_wattn_single_supports", "prb_wattn_single"):
         getattr(h, name).restype = c_int
     for name in ("prb_embed_scaled", "prb_route_scores", "prb_routed_act", "prb_retention_lanes",
                  "prb_retention_scan", "prb_retention_finish", "prb_diff_prepare",
@@ -1480,14 +1490,37 @@ def tmix_shift(out, h, prev_state, mu, seq_of_token, positions, q_start, state_s
                                 _stream()), what)
 
 
+def tmix_step_supports(dim: int, vdim: int) -> bool:
+    """Whether :func:`tmix_scan` takes ``finish`` for these head sizes (a CTA then holds all of a
+    head's value columns)."""
+    return bool(lib().prb_tmix_step_supports(int(dim), int(vdim)))
+
+
+def tmix_segment() -> int:
+    """Tokens a segment of the segmented scan."""
+    return int(lib().prb_tmix_segment())
+
+
+def tmix_max_segments(t_cap: int, b_cap: int) -> int:
+    """Segments a step of at most ``t_cap`` tokens in ``b_cap`` requests can have."""
+    return int(lib().prb_tmix_max_segments(int(t_cap), int(b_cap)))
+
+
 def tmix_scan(raw, proj, r_col: int, k_col: int, v_col: int, lr_col: int, w2, w0, u, state, h,
               prev_state, q_start, state_slot, positions, n_requests: int, heads: int, dim: int,
-              vdim: int, status=None) -> None:
+              vdim: int, status=None, segments=None, w_col: int = -1, finish=None) -> None:
     """The recurrence over the step's tokens, request by request: per head o_t = (S + diag(u)
     k_t v_t^T)^T r_t, then S <- diag(w_t) S + k_t v_t^T with w_t = exp(-exp(w0 + w2 tanh(lr_t)));
     r, k, v and lr are column ranges of ``proj`` (float32).  ``state`` [slots, heads, vdim, dim]
     float32 is read (zero at position 0) and written back; ``prev_state`` [slots, width]
-    receives the request's last row of ``h``.  raw float32 [T, heads * vdim]."""
+    receives the request's last row of ``h``.  raw float32 [T, heads * vdim].
+
+    ``segments`` (own, start, decay), workspaces [n, heads, vdim, dim] twice and [n, heads,
+    dim] with n >= tmix_max_segments(T, n_requests): portions are cut into segments of
+    tmix_segment() tokens that run side by side, and the decays are left in proj's columns
+    from ``w_col``.  ``finish`` (out, g_col, norm_w, eps, out_scale): the scan applies
+    :func:`tmix_finish` itself and writes ``out`` instead of ``raw`` (sizes that
+    :func:`tmix_step_supports` takes; not with ``segments``)."""
     what = "tmix_scan"
     for name, t in (("raw", raw), ("w2", w2), ("w0", w0), ("u", u), ("state", state)):
         _need(t, torch.float32, name, what)
@@ -1504,11 +1537,39 @@ def tmix_scan(raw, proj, r_col: int, k_col: int, v_col: int, lr_col: int, w2, w0
             prev_state.dtype != h.dtype or prev_state.shape != (state.shape[0], width) or \
             h.stride(1) != 1 or q_start.numel() < n_requests + 1:
         raise KernelArgumentError(f"{what}: shapes or types do not fit")
+    if segments is not None:
+        own, start, decay = segments
+        n = own.shape[0]
+        for name, t in (("segments' own sums", own), ("segments' starts", start),
+                        ("segments' decays", decay)):
+            _need(t, torch.float32, name, what)
+        if finish is not None or w_col < 0 or w_col + heads * dim > proj.shape[1] or \
+                tuple(own.shape) != (n, heads, vdim, dim) or tuple(start.shape) != tuple(own.shape) \
+                or tuple(decay.shape) != (n, heads, dim) or \
+                not (own.is_contiguous() and start.is_contiguous() and decay.is_contiguous()):
+            raise KernelArgumentError(f"{what}: the segments' workspaces do not fit")
+        _check(lib().prb_tmix_scan_segments(
+            _p(raw), raw.stride(0), _p(proj), proj.stride(0), int(r_col), int(k_col), int(v_col),
+            int(lr_col), int(w_col), _p(w2), _p(w0), _p(u), _p(state), _p(h), h.stride(0),
+            _p(prev_state), _p(q_start), _p(state_slot), _p(positions), proj.shape[0],
+            int(n_requests), heads, dim, vdim, rank, width, state.shape[0], dtype_code(h.dtype),
+            _p(own), _p(start), _p(decay), n, _p(status), _stream()), what)
+        return
+    out, out_ld, g_col, norm_w, eps, out_scale = None, 0, 0, None, 0.0, 1.0
+    if finish is not None:
+        out, g_col, norm_w, eps, out_scale = finish
+        _need(norm_w, torch.float32, "norm_w", what)
+        if out.dtype != h.dtype or out.stride(1) != 1 or out.shape[0] < proj.shape[0] or \
+                out.shape[1] < heads * vdim or g_col + heads * vdim > proj.shape[1] or \
+                norm_w.numel() != heads * vdim:
+            raise KernelArgumentError(f"{what}: the finish's tensors do not fit")
+        out_ld = out.stride(0)
     _check(lib().prb_tmix_scan(_p(raw), raw.stride(0), _p(proj), proj.stride(0), int(r_col),
                                int(k_col), int(v_col), int(lr_col), _p(w2), _p(w0), _p(u), _p(state),
                                _p(h), h.stride(0), _p(prev_state), _p(q_start), _p(state_slot),
                                _p(positions), int(n_requests), heads, dim, vdim, rank, width,
-                               state.shape[0], dtype_code(h.dtype), _p(status), _stream()), what)
+                               state.shape[0], dtype_code(h.dtype), _p(status), _p(out), out_ld,
+                               int(g_col), _p(norm_w), float(eps), float(out_scale), _stream()), what)
 
 
 def tmix_finish(out, raw, proj, g_col: int, norm_w, seq_of_token, heads: int, vdim: int,
@@ -1576,14 +1637,21 @@ def wattn_tile_rows(heads: int, kv_heads: int, dim: int, vdim: int) -> int:
     return int(lib().prb_wattn_tile_rows(heads, kv_heads, dim, vdim))
 
 
+def wattn_single_supports(heads: int, kv_heads: int, dim: int, vdim: int) -> bool:
+    """Whether the single-token kernel takes these sizes."""
+    return bool(lib().prb_wattn_single_supports(heads, kv_heads, dim, vdim))
+
+
 def wattn(out, q, cache, block_table, seq_of_token, positions, heads: int, dim: int, vdim: int,
           window: int, keep_first: int, scale: float, gate=None, slopes=None,
-          out_scale: float = 1.0, status=None, tile_rows: int = 0) -> None:
+          out_scale: float = 1.0, status=None, tile_rows: int = 0, single: bool = False) -> None:
     """Softmax attention over cache rows [k | v]: a query at position i sees key j <= i with
     i - j < window (``window`` 0: all) or j < keep_first; score (q . k) * scale - slopes[h] * (i
     - j); head h's result times sigmoid(gate[t, h]) (``gate``: float32, may be a column slice)
     times ``out_scale``.  32-bit arithmetic; out in the cache's type.  ``tile_rows`` > 0: the
-    tiled kernel (a CTA per that many consecutive token rows and key/value head)."""
+    tiled kernel (a CTA per that many consecutive token rows and key/value head).  ``single``:
+    the kernel for steps of single tokens (a CTA per (token, key/value head) whose warps share
+    out the key blocks; sizes that :func:`wattn_single_supports` takes)."""
     what = "wattn"
     _need(q, torch.float32, "q", what)
     _need(cache, None, "cache", what)
@@ -1610,7 +1678,9 @@ def wattn(out, q, cache, block_table, seq_of_token, positions, heads: int, dim: 
               page_size, block_table.shape[1], pages, int(window or 0), int(keep_first or 0))
     tail = (float(scale), float(out_scale), dtype_code(cache.dtype), dtype_code(out.dtype),
             _p(status), _stream())
-    if tile_rows > 0:
+    if single:
+        _check(lib().prb_wattn_single(*common, *tail), what)
+    elif tile_rows > 0:
         _check(lib().prb_wattn_tile(*common, int(tile_rows), *tail), what)
     else:
         _check(lib().prb_wattn(*common, *tail), what)

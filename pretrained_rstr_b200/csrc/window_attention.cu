@@ -429,6 +429,220 @@ wattn_tile_kernel(O* __restrict__ out, long out_ld, const float* __restrict__ q,
     }
 }
 
+// ------------------------------------------------------------ the single-token kernel
+// A CTA per (token, key/value head) for steps whose requests bring one token each.  The key
+// blocks of the tiled kernel (32 ABSOLUTE positions; the kept first tokens' before the
+// window's) are dealt to the CTA's warps round by round: a round stages one block per warp in
+// shared memory with all threads loading, then every warp scores its own block for all query
+// heads of the key/value head (a lane a key) and adds its values to sums of its own.  The
+// warps' states (maximum, sum, weighted values) are joined at the end in warp order.
+constexpr int WS_MAX_PPW = 8;        // query heads a key/value head at most
+
+template <typename C, typename O, int VC, int PPW>
+__global__ void __launch_bounds__(WT_WARPS * 32)
+wattn_single_kernel(O* __restrict__ out, long out_ld, const float* __restrict__ q,
+                    const C* __restrict__ cache, const int* __restrict__ block_table,
+                    const int* __restrict__ seq_of_token, const int* __restrict__ positions,
+                    const float* __restrict__ gate, long gate_ld, const float* __restrict__ slopes,
+                    int n_tokens, int heads, int kv_heads, int dim, int vdim, int page_size,
+                    int max_pages, int num_pages, int window, int keep_first, float scale,
+                    float out_scale, int* status) {
+    extern __shared__ __align__(16) float smem[];
+    __shared__ long long rows_s[WT_WARPS * WT_KB];   // a staged key's row of the cache, or -1
+    prb_grid_launch_dependents();
+    const int nw = blockDim.x >> 5;                  // warps: key blocks a round
+    const int hg = heads / kv_heads;
+    const int g = blockIdx.y, r = blockIdx.x;
+    const int rowlen = dim + vdim;
+    const int kpitch = dim + 1;                      // odd: lanes read their own key's row
+    const int qpitch = (dim + 3) / 4 * 4;
+    const int keys = nw * WT_KB;
+    const int jpitch = 2 + vdim;
+    float* Ks = smem;                                // [keys][kpitch]
+    float* Vs = Ks + (keys * kpitch + 3) / 4 * 4;    // [keys][vdim]
+    float* Qs = Vs + (keys * vdim + 3) / 4 * 4;      // [hg][qpitch]
+    float* Js = Qs + hg * qpitch;                    // [nw][hg][2 + vdim]
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    O* orow = out + (size_t)r * out_ld + (size_t)g * hg * vdim;
+    const int b = seq_of_token[r];
+    const int p = b < 0 ? 0 : positions[r];
+    if (b < 0 || p < 0 || p >= max_pages * page_size) {          // a padding row, or a bad one
+        if (b >= 0 && threadIdx.x == 0)
+            prb_set_status(status, PRB_S_POSITION_RANGE, r, p, max_pages * page_size);
+        for (int j = threadIdx.x; j < hg * vdim; j += blockDim.x) orow[j] = prb_from_float<O>(0.0f);
+        return;
+    }
+    const int win = window > 0 ? window : NO_WINDOW;
+    const int lo_min = max(0, p - win + 1);
+    const int win_start = (lo_min / WT_KB) * WT_KB;
+    const int first_end = min(keep_first, win_start);
+    const int first_blocks = (first_end + WT_KB - 1) / WT_KB;
+    const int n_blocks = first_blocks + (p - win_start) / WT_KB + 1;
+    const int* table = block_table + (size_t)b * max_pages;
+    for (int e = threadIdx.x; e < hg * dim; e += blockDim.x) {
+        const int hh = e / dim, d = e - hh * dim;
+        Qs[hh * qpitch + d] = q[((size_t)r * heads + g * hg + hh) * dim + d] * scale;
+    }
+    float acc[PPW][VC];
+    float m[PPW], l[PPW], slope[PPW];
+#pragma unroll
+    for (int x = 0; x < PPW; ++x) {
+        m[x] = -INFINITY;
+        l[x] = 0.0f;
+        slope[x] = (slopes && x < hg) ? slopes[g * hg + x] : 0.0f;
+#pragma unroll
+        for (int c = 0; c < VC; ++c) acc[x][c] = 0.0f;
+    }
+    for (int blk0 = 0; blk0 < n_blocks; blk0 += nw) {
+        __syncthreads();                             // the round before has been consumed
+        for (int kk = threadIdx.x; kk < keys; kk += blockDim.x) {
+            const int blk = blk0 + kk / WT_KB;
+            long long row = -1;
+            if (blk < n_blocks) {
+                const int j0 = blk < first_blocks ? blk * WT_KB : win_start + (blk - first_blocks) * WT_KB;
+                const int j_end = blk < first_blocks ? first_end : p + 1;
+                const int jj = j0 + kk % WT_KB;
+                // (only keys the query may see are fetched)
+                if (jj < j_end && (jj >= lo_min || jj < keep_first)) {
+                    const int pg = table[jj / page_size];
+                    if (pg < 0 || pg >= num_pages) prb_set_status(status, PRB_S_PAGE_RANGE, r, jj, pg);
+                    else row = ((long long)pg * kv_heads + g) * page_size + jj % page_size;
+                }
+            }
+            rows_s[kk] = row;
+        }
+        __syncthreads();
+        constexpr int VE = 16 / (int)sizeof(C);
+        if (rowlen % VE == 0 && dim % VE == 0) {
+            const int nv = rowlen / VE;
+#pragma unroll 4
+            for (int e = threadIdx.x; e < keys * nv; e += blockDim.x) {
+                const int kk = e / nv, vi = e - kk * nv;
+                const long long row = rows_s[kk];
+                uint4 raw = make_uint4(0u, 0u, 0u, 0u);
+                if (row >= 0) raw = *reinterpret_cast<const uint4*>(cache + (size_t)row * rowlen + vi * VE);
+                const C* vals = reinterpret_cast<const C*>(&raw);
+                const int off = vi * VE;
+                float* dst = off < dim ? Ks + kk * kpitch + off : Vs + kk * vdim + off - dim;
+#pragma unroll
+                for (int x = 0; x < VE; ++x) dst[x] = prb_to_float<C>(vals[x]);
+            }
+        } else {
+            for (int e = threadIdx.x; e < keys * rowlen; e += blockDim.x) {
+                const int kk = e / rowlen, off = e - kk * rowlen;
+                const long long row = rows_s[kk];
+                const float val = row < 0 ? 0.0f : prb_to_float<C>(cache[(size_t)row * rowlen + off]);
+                if (off < dim) Ks[kk * kpitch + off] = val;
+                else Vs[kk * vdim + off - dim] = val;
+            }
+        }
+        __syncthreads();
+        const int blk = blk0 + warp;
+        if (blk >= n_blocks) continue;
+        const int j0 = blk < first_blocks ? blk * WT_KB : win_start + (blk - first_blocks) * WT_KB;
+        const int j_end = blk < first_blocks ? first_end : p + 1;
+        const int k_hi = min(min(WT_KB, j_end - j0), p - j0 + 1);
+        if (k_hi <= 0) continue;
+        const int j = j0 + lane;
+        const float* krow = Ks + (warp * WT_KB + lane) * kpitch;
+        const float* vblk = Vs + (size_t)warp * WT_KB * vdim;
+        float s[PPW];
+#pragma unroll
+        for (int x = 0; x < PPW; ++x) s[x] = 0.0f;
+        if (dim % 4 == 0) {
+            for (int d = 0; d < dim; d += 4) {
+                const float a0 = krow[d], a1 = krow[d + 1], a2 = krow[d + 2], a3 = krow[d + 3];
+#pragma unroll
+                for (int x = 0; x < PPW; ++x) {
+                    if (x < hg) {
+                        const float4 u = *reinterpret_cast<const float4*>(Qs + x * qpitch + d);
+                        s[x] = fmaf(u.w, a3, fmaf(u.z, a2, fmaf(u.y, a1, fmaf(u.x, a0, s[x]))));
+                    }
+                }
+            }
+        } else {
+            for (int d = 0; d < dim; ++d) {
+                const float a0 = krow[d];
+#pragma unroll
+                for (int x = 0; x < PPW; ++x)
+                    if (x < hg) s[x] = fmaf(Qs[x * qpitch + d], a0, s[x]);
+            }
+        }
+        const bool vis = j < j_end && j <= p && (p - j < win || j < keep_first);
+        float e[PPW];
+#pragma unroll
+        for (int x = 0; x < PPW; ++x) {
+            e[x] = 0.0f;
+            if (x >= hg) continue;
+            const float tt = vis ? s[x] - slope[x] * (float)(p - j) : -INFINITY;
+            const float nm = fmaxf(m[x], prb_warp_max(tt));
+            if (nm == -INFINITY) continue;           // (no key of the block is seen)
+            const float f = expf(m[x] - nm);         // (exp(-inf) = 0)
+            e[x] = vis ? expf(tt - nm) : 0.0f;
+            l[x] = l[x] * f + prb_warp_sum(e[x]);
+            m[x] = nm;
+#pragma unroll
+            for (int c = 0; c < VC; ++c) acc[x][c] *= f;
+        }
+        for (int kk = 0; kk < k_hi; ++kk) {
+            float v[VC];
+#pragma unroll
+            for (int c = 0; c < VC; ++c) v[c] = (lane + 32 * c < vdim) ? vblk[kk * vdim + lane + 32 * c] : 0.0f;
+#pragma unroll
+            for (int x = 0; x < PPW; ++x) {
+                const float w = __shfl_sync(0xffffffffu, e[x], kk);
+#pragma unroll
+                for (int c = 0; c < VC; ++c) acc[x][c] = fmaf(w, v[c], acc[x][c]);
+            }
+        }
+    }
+    // the warps' states, then a thread per (head, value coordinate) joins them in warp order
+#pragma unroll
+    for (int x = 0; x < PPW; ++x) {
+        if (x >= hg) break;
+        float* st = Js + ((size_t)warp * hg + x) * jpitch;
+        if (lane == 0) {
+            st[0] = m[x];
+            st[1] = l[x];
+        }
+#pragma unroll
+        for (int c = 0; c < VC; ++c)
+            if (lane + 32 * c < vdim) st[2 + lane + 32 * c] = acc[x][c];
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < hg * vdim; e += blockDim.x) {
+        const int hh = e / vdim, jv = e - hh * vdim;
+        float top = -INFINITY;
+        for (int w = 0; w < nw; ++w) top = fmaxf(top, Js[((size_t)w * hg + hh) * jpitch]);
+        float lsum = 0.0f, a = 0.0f;
+        for (int w = 0; w < nw; ++w) {
+            const float* st = Js + ((size_t)w * hg + hh) * jpitch;
+            const float f = st[0] == -INFINITY ? 0.0f : expf(st[0] - top);
+            lsum = fmaf(st[1], f, lsum);
+            a = fmaf(st[2 + jv], f, a);
+        }
+        const int h = g * hg + hh;
+        const float gt = (gate ? wa_sigmoid(gate[(size_t)r * gate_ld + h]) : 1.0f) * out_scale;
+        orow[e] = prb_from_float<O>(lsum > 0.0f ? a / lsum * gt : 0.0f);
+    }
+}
+
+size_t ws_smem(int hg, int dim, int vdim, int nw) {
+    const int keys = nw * WT_KB;
+    return (size_t)((keys * (dim + 1) + 3) / 4 * 4 + (keys * vdim + 3) / 4 * 4 +
+                    hg * ((dim + 3) / 4 * 4) + nw * hg * (2 + vdim)) * sizeof(float);
+}
+
+// Warps (key blocks a round) of the single-token kernel for these sizes; 0: it does not take them.
+int ws_warps(int heads, int kv_heads, int dim, int vdim) {
+    if (heads <= 0 || kv_heads <= 0 || heads % kv_heads != 0) return 0;
+    const int hg = heads / kv_heads;
+    if (hg > WS_MAX_PPW || vdim > 32 * WT_VC || dim > 512) return 0;
+    for (int nw = WT_WARPS; nw >= 1; nw >>= 1)
+        if (ws_smem(hg, dim, vdim, nw) <= 200 * 1024) return nw;
+    return 0;
+}
+
 size_t wt_smem(int dim, int vdim) {
     return (size_t)((WT_KB * (dim + 1) + 3) / 4 * 4 + (WT_KB * vdim + 3) / 4 * 4 +
                     WT_WARPS * WT_PPW * ((dim + 3) / 4 * 4)) * sizeof(float);
@@ -536,6 +750,57 @@ PRB_API int prb_wattn_tile(void* out, long out_ld, const float* q, const void* c
     else return PRB_E_DTYPE;
 #undef WATT
 #undef WATT1
+    PRB_LAUNCH_CHECK();
+    return 0;
+}
+
+// 1 if the single-token kernel takes these sizes.
+PRB_API int prb_wattn_single_supports(int heads, int kv_heads, int dim, int vdim) {
+    return ws_warps(heads, kv_heads, dim, vdim) > 0 ? 1 : 0;
+}
+
+PRB_API int prb_wattn_single(void* out, long out_ld, const float* q, const void* cache,
+                             const int* block_table, const int* seq_of_token, const int* positions,
+                             const float* gate, long gate_ld, const float* slopes, int n_tokens,
+                             int heads, int kv_heads, int dim, int vdim, int page_size,
+                             int max_pages, int num_pages, int window, int keep_first, float scale,
+                             float out_scale, int cache_dtype, int out_dtype, int* status,
+                             cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    const int nw = ws_warps(heads, kv_heads, dim, vdim);
+    if (nw <= 0 || kv_heads > 65535 || page_size <= 0 || max_pages <= 0 || window < 0 ||
+        keep_first < 0)
+        return PRB_E_SIZE;
+    const int hg = heads / kv_heads;
+    const size_t smem = ws_smem(hg, dim, vdim, nw);
+    dim3 grid(n_tokens, kv_heads);
+#define WS2(CT, OT, VCN, PN)                                                                     \
+    do {                                                                                         \
+        if (smem > 48 * 1024)                                                                    \
+            cudaFuncSetAttribute(wattn_single_kernel<CT, OT, VCN, PN>,                           \
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);        \
+        wattn_single_kernel<CT, OT, VCN, PN><<<grid, nw * 32, smem, stream>>>(                   \
+            (OT*)out, out_ld, q, (const CT*)cache, block_table, seq_of_token, positions, gate,   \
+            gate_ld, slopes, n_tokens, heads, kv_heads, dim, vdim, page_size, max_pages,         \
+            num_pages, window, keep_first, scale, out_scale, status);                            \
+    } while (0)
+#define WS1(CT, OT, VCN)                                                                         \
+    do {                                                                                         \
+        if (hg <= 2) WS2(CT, OT, VCN, 2);                                                        \
+        else if (hg <= 4) WS2(CT, OT, VCN, 4);                                                   \
+        else WS2(CT, OT, VCN, 8);                                                                \
+    } while (0)
+#define WS(CT, OT)                                                                               \
+    do {                                                                                         \
+        if (vdim <= 64) WS1(CT, OT, 2);                                                          \
+        else WS1(CT, OT, 4);                                                                     \
+    } while (0)
+    if (cache_dtype == PRB_F32 && out_dtype == PRB_F32) WS(float, float);
+    else if (cache_dtype == PRB_BF16 && out_dtype == PRB_BF16) WS(__nv_bfloat16, __nv_bfloat16);
+    else return PRB_E_DTYPE;
+#undef WS
+#undef WS1
+#undef WS2
     PRB_LAUNCH_CHECK();
     return 0;
 }

@@ -73,7 +73,9 @@ class TimeMix(Mixer):
             self.linear[s] = Linear(mats[s], None, runtime)
             self.cols[s] = (at, mats[s].shape[0])
             at += _pad8(mats[s].shape[0])
-        self.proj_width = at
+        self.cols["decay"] = (at, hk)                # the segmented scan leaves the decays here
+        self.proj_width = at + _pad8(hk)
+        self.one_launch = torch.cuda.is_available() and ops.tmix_step_supports(self.dim, self.vdim)
         f32 = lambda t: t.to(torch.float32).contiguous()
         self.mu = torch.stack([f32(need("mu_" + s, (self.width,))) for s in _BLENDS]).contiguous()
         self.w2 = f32(need("w2", (hk, self.rank)))
@@ -99,11 +101,30 @@ class TimeMix(Mixer):
             self.linear[s].forward(ctx, blends[:, i * self.width:(i + 1) * self.width],
                                    proj[:, at:at + n])
         raw = ctx.scratch("tmix_raw", (cap, self.heads * self.vdim), torch.float32)[:t]
-        ops.tmix_scan(raw, proj, self.cols["r"][0], self.cols["k"][0], self.cols["v"][0],
-                      self.cols["w"][0], self.w2, self.w0, self.u, state, h, prev, ctx.q_start,
-                      ctx.state_slot, ctx.positions, ctx.layout.b_cap, self.heads, self.dim,
-                      self.vdim, ctx.status)
         gated = ctx.scratch_zero("tmix_gated", (cap, self.out.n_in), self.runtime.dtype)[:t]
+        requests = ctx.layout.b_cap
+        scan = lambda **kw: ops.tmix_scan(
+            raw, proj, self.cols["r"][0], self.cols["k"][0], self.cols["v"][0], self.cols["w"][0],
+            self.w2, self.w0, self.u, state, h, prev, ctx.q_start, ctx.state_slot, ctx.positions,
+            requests, self.heads, self.dim, self.vdim, ctx.status, **kw)
+        if ctx.layout.t_cap <= ops.tmix_segment():
+            # a step of few tokens: a CTA per (head, request) from and to the slot, with the
+            # finish inside where it holds all of the head's columns
+            if self.one_launch:
+                scan(finish=(gated, self.cols["g"][0], self.norm, self.eps, self.out_scale))
+                self.out.forward(ctx, gated, x, resid=x if accumulate else None)
+                return
+            scan()
+        else:
+            # portions are cut into segments that run side by side (workspaces sized once, for
+            # the largest step the runtime takes)
+            n = ops.tmix_max_segments(max(ctx.runtime.max_batched_tokens, ctx.layout.t_cap),
+                                      max(ctx.runtime.max_requests, requests))
+            shape = (n, self.heads, self.vdim, self.dim)
+            scan(segments=(ctx.scratch("tmix_seg_own", shape, torch.float32),
+                           ctx.scratch("tmix_seg_start", shape, torch.float32),
+                           ctx.scratch("tmix_seg_decay", (n, self.heads, self.dim), torch.float32)),
+                 w_col=self.cols["decay"][0])
         ops.tmix_finish(gated, raw, proj, self.cols["g"][0], self.norm, ctx.seq_of_token,
                         self.heads, self.vdim, self.eps, self.out_scale)
         self.out.forward(ctx, gated, x, resid=x if accumulate else None)

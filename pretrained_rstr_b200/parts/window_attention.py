@@ -92,8 +92,9 @@ class WindowAttention(Mixer):
                                         for h in range(self.heads)],
                                        dtype=torch.float64).to(torch.float32).to(dev)
         self.freq = rotary_frequencies(float(p.get("rot_base", 10000.0)), self.rot_dims, dev)
-        self.tile_rows = ops.wattn_tile_rows(self.heads, self.kv_heads, self.dim, self.vdim) \
-            if torch.cuda.is_available() else 0
+        gpu = torch.cuda.is_available()
+        self.tile_rows = ops.wattn_tile_rows(self.heads, self.kv_heads, self.dim, self.vdim) if gpu else 0
+        self.single_ok = gpu and ops.wattn_single_supports(self.heads, self.kv_heads, self.dim, self.vdim)
 
     def kv_spec(self) -> KVSpec:
         return KVSpec(self.kv_heads, self.dim + self.vdim, None, values=False)
@@ -121,13 +122,16 @@ class WindowAttention(Mixer):
                           self.heads, self.kv_heads, self.dim, self.vdim, self.rot_dims, self.eps,
                           self.temp_coef, self.temp_every, ctx.status)
         o = ctx.scratch_zero("wattn_out", (cap, self.out.n_in), self.runtime.dtype)[:t]
-        # a step of single tokens: a row a CTA (rows of different requests share no keys)
+        # a step of single tokens: a CTA per (token, key/value head) whose warps share out the
+        # key blocks (rows of different requests share no keys); sizes that kernel does not
+        # take: the tiled kernel, a row a CTA
         single = ctx.max_q_len == 1 or ctx.layout.t_cap <= ctx.layout.b_cap
         ops.wattn(o, q, cache.k, group.block_table, ctx.seq_of_token, ctx.positions, self.heads,
                   self.dim, self.vdim, self.window, self.keep_first, self.scale,
                   gate=proj[:, cols["gate"][0]:] if self.gated else None, slopes=self.slopes,
                   out_scale=self.out_scale, status=ctx.status,
-                  tile_rows=min(self.tile_rows, 1) if single else self.tile_rows)
+                  tile_rows=min(self.tile_rows, 1) if single else self.tile_rows,
+                  single=single and self.single_ok)
         self.out.forward(ctx, o, x, resid=x if accumulate else None)
 
 

@@ -77,8 +77,10 @@ class TimeMixCase:
         gd = gate.double()
         return P.unit_rms(o, eps) * self.norm_w.double().reshape(self.heads, self.vdim) * gd * torch.sigmoid(gd) * scale
 
-    def run(self, parts, eps, scale=1.0, out_dtype=torch.float32):
-        """parts: (slot, first position, r, k, v, gate, lr, h) per request of one step."""
+    def run(self, parts, eps, scale=1.0, out_dtype=torch.float32, mode="scan"):
+        """parts: (slot, first position, r, k, v, gate, lr, h) per request of one step.  ``mode``:
+        "scan" (a CTA per (head, request, columns) and the finish after it), "step" (the finish
+        inside the scan) or "segments" (portions cut into segments that run side by side)."""
         from pretrained_rstr_b200.csrc import ops
         hd, d, vd, rk = self.heads, self.dim, self.vdim, self.rank
         proj, pos, seq, qs, slots, hs = [], [], [], [0], [], []
@@ -86,7 +88,8 @@ class TimeMixCase:
             n = r.shape[0]
             pad = torch.zeros(n, 4)
             proj.append(torch.cat([pad, r.reshape(n, -1), k.reshape(n, -1), pad, v.reshape(n, -1),
-                                   gate.reshape(n, -1), pad, lr], dim=1))
+                                   gate.reshape(n, -1), pad, lr, pad, torch.full((n, hd * d), 77.0),
+                                   pad], dim=1))
             hs.append(h)
             pos += list(range(p0, p0 + n))
             seq += [b] * n
@@ -99,26 +102,48 @@ class TimeMixCase:
         v_col = 8 + 2 * hd * d
         g_col = v_col + hd * vd
         lr_col = g_col + hd * vd + 4
+        w_col = lr_col + rk + 4
         raw = torch.empty(t, hd * vd, device=DEV)
         status = torch.zeros(4, dtype=torch.int32, device=DEV)
+        out = torch.zeros(t, hd * vd + 8, dtype=out_dtype, device=DEV)
+        if out_dtype != torch.float32:
+            h_all, self.prev = h_all.to(out_dtype), self.prev.to(out_dtype)
+        extra = {}
+        if mode == "segments":
+            n = ops.tmix_max_segments(t, len(parts) + 1) + 2
+            extra = {"segments": (torch.full((n, hd, vd, d), 3.0, device=DEV),
+                                  torch.full((n, hd, vd, d), 3.0, device=DEV),
+                                  torch.full((n, hd, d), 3.0, device=DEV)), "w_col": w_col}
+        elif mode == "step":
+            extra = {"finish": (out, g_col, self.norm_w.to(DEV), eps, scale)}
         ops.tmix_scan(raw, proj, r_col, k_col, v_col, lr_col, self.w2.to(DEV), self.w0.to(DEV),
                       self.u.to(DEV).contiguous(), self.state, h_all, self.prev, _i32(qs + [qs[-1]]),
-                      _i32(slots + [0]), _i32(pos), len(parts) + 1, hd, d, vd, status)
+                      _i32(slots + [0]), _i32(pos), len(parts) + 1, hd, d, vd, status, **extra)
         assert int(status[0]) == 0, status.tolist()
-        out = torch.zeros(t, hd * vd + 8, dtype=out_dtype, device=DEV)
-        ops.tmix_finish(out, raw, proj, g_col, self.norm_w.to(DEV), _i32(seq), hd, vd, eps, scale)
+        if mode != "step":
+            ops.tmix_finish(out, raw, proj, g_col, self.norm_w.to(DEV), _i32(seq), hd, vd, eps, scale)
+        self.prev = self.prev.float()
         for (slot, *_rest, h), end in zip(parts, qs[1:]):
-            assert torch.equal(self.prev[slot].cpu(), h[-1])        # the row the next shift reads
+            assert torch.equal(self.prev[slot].cpu(), h[-1].to(out_dtype).float())   # the row the next shift reads
         return out.cpu().double()[:, :hd * vd].reshape(t, hd, vd)
 
 
+@pytest.mark.parametrize("mode", ["scan", "step", "segments"])
 @pytest.mark.parametrize("heads,dim,vdim,rank", [(3, 16, 16, 5), (2, 80, 80, 16), (1, 8, 136, 3),
-                                                 (2, 64, 64, 32), (1, 160, 16, 8), (4, 40, 24, 1)])
-def test_time_mix_kernels(heads, dim, vdim, rank):
-    """A whole sequence at once, in portions down to one token, beside another request; a
-    slot's earlier state is not read at position 0 and is carried from then on."""
+                                                 (2, 64, 64, 32), (1, 160, 16, 8), (4, 40, 24, 1),
+                                                 (1, 264, 40, 2), (2, 3, 5, 4)])
+def test_time_mix_kernels(heads, dim, vdim, rank, mode):
+    """A whole sequence at once, in portions down to one token and longer than a segment, beside
+    another request; a slot's earlier state is not read at position 0 and is carried from then
+    on.  Each way the scan runs: a CTA per request's portion with the finish after it or inside,
+    and in segments side by side."""
+    from pretrained_rstr_b200.csrc import ops
+    if mode == "step" and not ops.tmix_step_supports(dim, vdim):
+        pytest.skip("a head's columns do not fit one CTA")
     case = TimeMixCase(heads, dim, vdim, rank, seed=heads + dim)
-    n = 90
+    run = lambda parts, *a, **kw: TimeMixCase.run(case, parts, *a, mode=mode, **kw)
+    case.run = run
+    n = 290
     a = case.rows(n)
     b = case.rows(37)
     want, want2 = case.plain(*a[:5], 1e-5, 0.9), case.plain(*b[:5], 1e-5, 0.9)
@@ -126,7 +151,7 @@ def test_time_mix_kernels(heads, dim, vdim, rank):
     assert torch.allclose(got, want, atol=3e-5, rtol=3e-5)
     at, outs = 0, []
     cut = lambda rows, lo, hi: tuple(x[lo:hi] for x in rows)
-    for size in (1, 2, 17, 1, 33, 16, 20):
+    for size in (1, 2, 17, 1, 33, 16, 20, 64, 71, 65):
         part = (1, at, *cut(a, at, at + size))
         m = 1 + at % 7
         other = (2, 0, *cut(b, 0, m))
@@ -143,12 +168,15 @@ def test_time_mix_kernels(heads, dim, vdim, rank):
     assert torch.allclose(out16, want2, atol=3e-2, rtol=3e-2)
 
 
-def test_time_mix_far_token_stands_out():
+@pytest.mark.parametrize("mode", ["scan", "step", "segments"])
+def test_time_mix_far_token_stands_out(mode):
     """One key far back, made large, among hundreds: where the decay is slow it still carries
     the result, through a portion's start and through single tokens, and where it is fast it is
     gone; a lost state, a decay applied before the read, or a bonus that outlives its token
     would show."""
     case = TimeMixCase(2, 16, 16, 4, seed=9)
+    run = lambda parts, *a, **kw: TimeMixCase.run(case, parts, *a, mode=mode, **kw)
+    case.run = run
     case.w2.zero_()
     case.w0[:16] = -7.0                  # head 0: w = exp(-exp(-7)) ~ 0.9991
     case.w0[16:] = 0.0                   # head 1: w = exp(-1) ~ 0.37
@@ -239,7 +267,8 @@ class WindowCase:
     def run(self, queries, heads, window, keep_first, scale, gate=None, slopes=None, out_scale=1.0,
             tile_rows=0):
         """queries: (request, position, q [heads, dim]); returns kernel and plain results
-        [n, heads, vdim].  ``tile_rows`` 0: a CTA per (token, head); else the tiled kernel."""
+        [n, heads, vdim].  ``tile_rows`` 0: a CTA per (token, head); -1: the single-token
+        kernel; else the tiled kernel."""
         from pretrained_rstr_b200.csrc import ops
         n = len(queries)
         q = torch.stack([x for _, _, x in queries]).reshape(n, -1).to(DEV).contiguous()
@@ -253,7 +282,8 @@ class WindowCase:
         ops.wattn(out, q, self.cache, self.table, _i32([b for b, _, _ in queries]),
                   _i32([p for _, p, _ in queries]), heads, self.dim, self.vdim, window, keep_first,
                   scale, gate=gate_dev, slopes=None if slopes is None else slopes.float().to(DEV),
-                  out_scale=out_scale, status=status, tile_rows=tile_rows)
+                  out_scale=out_scale, status=status, tile_rows=max(tile_rows, 0),
+                  single=tile_rows < 0)
         assert int(status[0]) == 0, status.tolist()
         want = []
         for i, (b, p, x) in enumerate(queries):
@@ -272,7 +302,8 @@ class WindowCase:
 def _tile_choices(heads, kv_heads, dim, vdim):
     from pretrained_rstr_b200.csrc import ops
     most = ops.wattn_tile_rows(heads, kv_heads, dim, vdim)      # 0: the tiled kernel does not take them
-    return [0] + (sorted({1, min(5, most), most}) if most else [])
+    single = [-1] if ops.wattn_single_supports(heads, kv_heads, dim, vdim) else []
+    return [0] + single + (sorted({1, min(5, most), most}) if most else [])
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
