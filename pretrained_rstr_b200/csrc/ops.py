@@ -184,7 +184,7 @@ def _declare(h: ctypes.CDLL) -> None:
     h.prb_tmix_step_supports.argtypes = [I, I]
     h.prb_tmix_segment.argtypes = []
     h.prb_tmix_max_segments.argtypes = [I, I]
-    h.prb_tmix_scan_segments.argtypes = [P, L, P, L, I, I, I, I, I, P, P, P, P, P, L, P, P, P, P,
+    h.prb_tmix_scan_segments.argtypes = [P, L, P, L, I, I, I, I, P, L, P, P, P, P, P, L, P, P, P, P,
                                          I, I, I, I, I, I, I, I, I, P, P, P, I, P, P]
     h.prb_tmix_finish.argtypes = [P, L, P, L, P, L, I, P, P, I, I, I, F, F, I, P]
     h.prb_wattn_prepare.argtypes = [P, P, P, L, I, I, I, P, P, P, P, P, I, I, I, I, I, I, F, F, I,
@@ -1472,17 +1472,19 @@ def tmix_shift(out, h, prev_state, mu, seq_of_token, positions, q_start, state_s
     """The blends of a token's input with the previous token's: out[t, s * width + i] =
     h[t, i] + (h[t - 1, i] - h[t, i]) * mu[s, i] for each of mu's rows s.  The row before a
     request's first token of the step is the request's row of ``prev_state`` [slots, width]
-    (zeros at position 0)."""
+    (zeros at position 0).  ``mu`` None: out[t] = [h[t] | h[t - 1] - h[t]]."""
     what = "tmix_shift"
-    _need(mu, torch.float32, "mu", what)
+    if mu is not None:
+        _need(mu, torch.float32, "mu", what)
     for name, t in (("seq_of_token", seq_of_token), ("positions", positions),
                     ("q_start", q_start), ("state_slot", state_slot)):
         _need(t, torch.int32, name, what)
     n, width = h.shape
-    n_mix = mu.shape[0]
+    n_mix = 2 if mu is None else mu.shape[0]
     if not h.is_cuda or h.stride(1) != 1 or out.dtype != h.dtype or prev_state.dtype != h.dtype or \
             out.stride(1) != 1 or out.shape[0] < n or out.shape[1] < n_mix * width or \
-            mu.shape[1] != width or prev_state.shape[1] != width or not prev_state.is_contiguous():
+            (mu is not None and mu.shape[1] != width) or prev_state.shape[1] != width or \
+            not prev_state.is_contiguous():
         raise KernelArgumentError(f"{what}: shapes or types do not fit")
     _check(lib().prb_tmix_shift(_p(out), out.stride(0), _p(h), h.stride(0), _p(prev_state), _p(mu),
                                 _p(seq_of_token), _p(positions), _p(q_start), _p(state_slot), n,
@@ -1508,7 +1510,7 @@ def tmix_max_segments(t_cap: int, b_cap: int) -> int:
 
 def tmix_scan(raw, proj, r_col: int, k_col: int, v_col: int, lr_col: int, w2, w0, u, state, h,
               prev_state, q_start, state_slot, positions, n_requests: int, heads: int, dim: int,
-              vdim: int, status=None, segments=None, w_col: int = -1, finish=None) -> None:
+              vdim: int, status=None, segments=None, decays=None, finish=None) -> None:
     """The recurrence over the step's tokens, request by request: per head o_t = (S + diag(u)
     k_t v_t^T)^T r_t, then S <- diag(w_t) S + k_t v_t^T with w_t = exp(-exp(w0 + w2 tanh(lr_t)));
     r, k, v and lr are column ranges of ``proj`` (float32).  ``state`` [slots, heads, vdim, dim]
@@ -1517,8 +1519,8 @@ def tmix_scan(raw, proj, r_col: int, k_col: int, v_col: int, lr_col: int, w2, w0
 
     ``segments`` (own, start, decay), workspaces [n, heads, vdim, dim] twice and [n, heads,
     dim] with n >= tmix_max_segments(T, n_requests): portions are cut into segments of
-    tmix_segment() tokens that run side by side, and the decays are left in proj's columns
-    from ``w_col``.  ``finish`` (out, g_col, norm_w, eps, out_scale): the scan applies
+    tmix_segment() tokens that run side by side, and ``decays`` float32 [T, heads * dim]
+    receives every token's decays.  ``finish`` (out, g_col, norm_w, eps, out_scale): the scan applies
     :func:`tmix_finish` itself and writes ``out`` instead of ``raw`` (sizes that
     :func:`tmix_step_supports` takes; not with ``segments``)."""
     what = "tmix_scan"
@@ -1543,14 +1545,17 @@ def tmix_scan(raw, proj, r_col: int, k_col: int, v_col: int, lr_col: int, w2, w0
         for name, t in (("segments' own sums", own), ("segments' starts", start),
                         ("segments' decays", decay)):
             _need(t, torch.float32, name, what)
-        if finish is not None or w_col < 0 or w_col + heads * dim > proj.shape[1] or \
+        _need(decays, torch.float32, "decays", what)
+        if finish is not None or decays.stride(1) != 1 or decays.shape[0] < proj.shape[0] or \
+                decays.shape[1] < heads * dim or \
                 tuple(own.shape) != (n, heads, vdim, dim) or tuple(start.shape) != tuple(own.shape) \
                 or tuple(decay.shape) != (n, heads, dim) or \
                 not (own.is_contiguous() and start.is_contiguous() and decay.is_contiguous()):
             raise KernelArgumentError(f"{what}: the segments' workspaces do not fit")
         _check(lib().prb_tmix_scan_segments(
             _p(raw), raw.stride(0), _p(proj), proj.stride(0), int(r_col), int(k_col), int(v_col),
-            int(lr_col), int(w_col), _p(w2), _p(w0), _p(u), _p(state), _p(h), h.stride(0),
+            int(lr_col), _p(decays), decays.stride(0), _p(w2), _p(w0), _p(u), _p(state), _p(h),
+            h.stride(0),
             _p(prev_state), _p(q_start), _p(state_slot), _p(positions), proj.shape[0],
             int(n_requests), heads, dim, vdim, rank, width, state.shape[0], dtype_code(h.dtype),
             _p(own), _p(start), _p(decay), n, _p(status), _stream()), what)

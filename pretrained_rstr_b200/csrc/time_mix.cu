@@ -11,7 +11,10 @@
 // then each head's o is brought to unit root-mean-square, multiplied by a weight per channel,
 // by silu(gate) and by a constant.
 //
-// tmix_shift: a CTA per token; writes the blends side by side, [T, n_mix * width].  The
+// tmix_shift: a CTA per token; writes the blends side by side, [T, n_mix * width], or (without
+//   mu) the row beside its difference from the previous one, [h_t | h_(t-1) - h_t]: a blend's
+//   projection is linear, W x_s = W h_t + (W diag(mu_s)) (h_(t-1) - h_t), so one product of that
+//   pair with [W | W diag(mu_s)] of all projections serves them all.  The
 //   previous row of a request's first token of the step is the request's state row (the
 //   input of its last token so far), or zeros at position 0.
 // tmix_scan: a CTA per (head, request, group of value columns).  A column of S is independent
@@ -59,6 +62,14 @@ __global__ void tmix_shift_kernel(A* __restrict__ out, long out_ld, const A* __r
                 prev = prev_state + (size_t)slot * width;
             }
         }
+    }
+    if (mu == nullptr) {                             // [h_t | h_(t-1) - h_t]
+        for (int i = threadIdx.x; i < width; i += blockDim.x) {
+            const float c = prb_to_float<A>(cur[i]);
+            o[i] = cur[i];
+            o[(size_t)width + i] = prb_from_float<A>((prev ? prb_to_float<A>(prev[i]) : 0.0f) - c);
+        }
+        return;
     }
     for (int i = threadIdx.x; i < width; i += blockDim.x) {
         const float c = prb_to_float<A>(cur[i]);
@@ -202,7 +213,7 @@ tmix_scan_kernel(float* __restrict__ raw, long raw_ld, const float* __restrict__
 
 // ------------------------------------------------------------- long portions in segments
 // Portions are cut into segments of TS_SEG tokens that run side by side:
-//   tmix_decay:        w_t = exp(-exp(w0 + W2 tanh(lr_t))) of every token into columns of proj;
+//   tmix_decay:        w_t = exp(-exp(w0 + W2 tanh(lr_t))) of every token into a buffer of its own;
 //   pass 1 (MODE 1):   every segment but a request's last builds, from zero, what its own tokens
 //                      add to the state, and the product of its decays per key channel;
 //   pass 2 (carry):    per request the states at the segments' starts, one after the other:
@@ -217,8 +228,9 @@ constexpr int TS_BLOCK = 16;         // tokens staged at a time
 
 struct SegArgs {
     float* raw; long raw_ld;
-    float* proj; long ld;
-    int r_col, k_col, v_col, lr_col, w_col;
+    const float* proj; long ld;
+    int r_col, k_col, v_col, lr_col;
+    float* decay; long decay_ld;                     // [T, heads * dim]: the decays of every token
     const float* w2; const float* w0; const float* u;
     float* state;
     const void* h; long h_ld; void* prev_state;
@@ -248,14 +260,14 @@ __global__ void tmix_decay_kernel(SegArgs a) {
     extern __shared__ float th[];
     prb_grid_launch_dependents();
     const int t = blockIdx.x;
-    float* row = a.proj + (size_t)t * a.ld;
+    const float* row = a.proj + (size_t)t * a.ld;
     for (int j = threadIdx.x; j < a.rank; j += blockDim.x) th[j] = tanhf(row[a.lr_col + j]);
     __syncthreads();
     for (int ch = threadIdx.x; ch < a.heads * a.dim; ch += blockDim.x) {
         const float* wr = a.w2 + (size_t)ch * a.rank;
         float z = a.w0[ch];
         for (int j = 0; j < a.rank; ++j) z = fmaf(wr[j], th[j], z);
-        row[a.w_col + ch] = expf(-expf(z));
+        a.decay[(size_t)t * a.decay_ld + ch] = expf(-expf(z));
     }
 }
 
@@ -309,7 +321,7 @@ __global__ void __launch_bounds__(1024) tmix_seg_kernel(SegArgs a) {
                 const float* row = a.proj + (size_t)(tb + tok) * a.ld + (size_t)hd * dim + kk;
                 if (MODE == 2) rr = row[a.r_col];
                 kx = row[a.k_col];
-                ww = row[a.w_col];
+                ww = a.decay[(size_t)(tb + tok) * a.decay_ld + (size_t)hd * dim + kk];
             }
             r_s[e] = rr;
             k_s[e] = kx;
@@ -517,11 +529,12 @@ PRB_API int prb_tmix_scan(float* raw, long raw_ld, const float* proj, long ld, i
 PRB_API int prb_tmix_segment() { return TS_SEG; }
 PRB_API int prb_tmix_max_segments(int t_cap, int b_cap) { return t_cap / TS_SEG + b_cap; }
 
-// The scan of long portions in segments: four launches.  proj's columns [w_col, w_col + heads *
-// dim) receive the decays; seg_own and seg_start [segments, heads, vdim, dim], seg_decay
-// [segments, heads, dim] are workspaces (segments >= prb_tmix_max_segments(n_tokens, n_requests)).
-PRB_API int prb_tmix_scan_segments(float* raw, long raw_ld, float* proj, long ld, int r_col,
-                                   int k_col, int v_col, int lr_col, int w_col, const float* w2,
+// The scan of long portions in segments: four launches.  decay [n_tokens, decay_ld] receives the
+// decays; seg_own and seg_start [segments, heads, vdim, dim], seg_decay [segments, heads, dim]
+// are workspaces (segments >= prb_tmix_max_segments(n_tokens, n_requests)).
+PRB_API int prb_tmix_scan_segments(float* raw, long raw_ld, const float* proj, long ld, int r_col,
+                                   int k_col, int v_col, int lr_col, float* decay, long decay_ld,
+                                   const float* w2,
                                    const float* w0, const float* u, float* state, const void* h,
                                    long h_ld, void* prev_state, const int* q_start,
                                    const int* state_slot, const int* positions, int n_tokens,
@@ -543,7 +556,7 @@ PRB_API int prb_tmix_scan_segments(float* raw, long raw_ld, float* proj, long ld
     const int groups = (vdim + cols - 1) / cols;
     const int threads = (cols * lanes + 31) / 32 * 32;
     const size_t smem = (size_t)TS_BLOCK * (3 * lanes * kpl + cols) * sizeof(float);
-    SegArgs a{raw, raw_ld, proj, ld, r_col, k_col, v_col, lr_col, w_col, w2, w0, u, state, h, h_ld,
+    SegArgs a{raw, raw_ld, proj, ld, r_col, k_col, v_col, lr_col, decay, decay_ld, w2, w0, u, state, h, h_ld,
               prev_state, q_start, state_slot, positions, n_tokens, n_requests, heads, dim, vdim,
               rank, width, lanes, cols, n_slots, seg_own, seg_start, seg_decay, status};
     tmix_decay_kernel<<<n_tokens, 256, (size_t)rank * sizeof(float), stream>>>(a);

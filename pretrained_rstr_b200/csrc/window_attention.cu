@@ -435,8 +435,24 @@ wattn_tile_kernel(O* __restrict__ out, long out_ld, const float* __restrict__ q,
 // window's) are dealt to the CTA's warps round by round: a round stages one block per warp in
 // shared memory with all threads loading, then every warp scores its own block for all query
 // heads of the key/value head (a lane a key) and adds its values to sums of its own.  The
-// warps' states (maximum, sum, weighted values) are joined at the end in warp order.
+// warps' states (maximum, sum, weighted values) are joined at the end in warp order.  Where
+// the step's tokens leave SMs idle, a (token, key/value head) is a thread-block cluster of
+// gridDim.z CTAs that take the rounds in turn; the cluster's first CTA joins all CTAs' warps
+// (in CTA, then warp order) through distributed shared memory.
 constexpr int WS_MAX_PPW = 8;        // query heads a key/value head at most
+
+__device__ __forceinline__ void ws_cluster_sync() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float ws_ld_cluster(const float* local, int rank) {
+    const uint32_t laddr = (uint32_t)__cvta_generic_to_shared(local);
+    uint32_t raddr;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(raddr) : "r"(laddr), "r"(rank));
+    float v;
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(raddr) : "memory");
+    return v;
+}
 
 template <typename C, typename O, int VC, int PPW>
 __global__ void __launch_bounds__(WT_WARPS * 32)
@@ -466,7 +482,9 @@ wattn_single_kernel(O* __restrict__ out, long out_ld, const float* __restrict__ 
     O* orow = out + (size_t)r * out_ld + (size_t)g * hg * vdim;
     const int b = seq_of_token[r];
     const int p = b < 0 ? 0 : positions[r];
+    const int splits = gridDim.z, split = blockIdx.z;            // the cluster and this CTA's rank
     if (b < 0 || p < 0 || p >= max_pages * page_size) {          // a padding row, or a bad one
+        if (split > 0) return;                                   // (so for the whole cluster)
         if (b >= 0 && threadIdx.x == 0)
             prb_set_status(status, PRB_S_POSITION_RANGE, r, p, max_pages * page_size);
         for (int j = threadIdx.x; j < hg * vdim; j += blockDim.x) orow[j] = prb_from_float<O>(0.0f);
@@ -493,7 +511,7 @@ wattn_single_kernel(O* __restrict__ out, long out_ld, const float* __restrict__ 
 #pragma unroll
         for (int c = 0; c < VC; ++c) acc[x][c] = 0.0f;
     }
-    for (int blk0 = 0; blk0 < n_blocks; blk0 += nw) {
+    for (int blk0 = split * nw; blk0 < n_blocks; blk0 += splits * nw) {
         __syncthreads();                             // the round before has been consumed
         for (int kk = threadIdx.x; kk < keys; kk += blockDim.x) {
             const int blk = blk0 + kk / WT_KB;
@@ -609,22 +627,32 @@ wattn_single_kernel(O* __restrict__ out, long out_ld, const float* __restrict__ 
         for (int c = 0; c < VC; ++c)
             if (lane + 32 * c < vdim) st[2 + lane + 32 * c] = acc[x][c];
     }
-    __syncthreads();
-    for (int e = threadIdx.x; e < hg * vdim; e += blockDim.x) {
-        const int hh = e / vdim, jv = e - hh * vdim;
-        float top = -INFINITY;
-        for (int w = 0; w < nw; ++w) top = fmaxf(top, Js[((size_t)w * hg + hh) * jpitch]);
-        float lsum = 0.0f, a = 0.0f;
-        for (int w = 0; w < nw; ++w) {
-            const float* st = Js + ((size_t)w * hg + hh) * jpitch;
-            const float f = st[0] == -INFINITY ? 0.0f : expf(st[0] - top);
-            lsum = fmaf(st[1], f, lsum);
-            a = fmaf(st[2 + jv], f, a);
+    if (splits > 1) ws_cluster_sync();               // every CTA's states are in place
+    else __syncthreads();
+    if (split == 0) {
+        for (int e = threadIdx.x; e < hg * vdim; e += blockDim.x) {
+            const int hh = e / vdim, jv = e - hh * vdim;
+            float top = -INFINITY;
+            for (int ss = 0; ss < splits; ++ss)
+                for (int w = 0; w < nw; ++w) {
+                    const float* st = Js + ((size_t)w * hg + hh) * jpitch;
+                    top = fmaxf(top, splits > 1 ? ws_ld_cluster(st, ss) : st[0]);
+                }
+            float lsum = 0.0f, a = 0.0f;
+            for (int ss = 0; ss < splits; ++ss)
+                for (int w = 0; w < nw; ++w) {
+                    const float* st = Js + ((size_t)w * hg + hh) * jpitch;
+                    const float mw = splits > 1 ? ws_ld_cluster(st, ss) : st[0];
+                    const float f = mw == -INFINITY ? 0.0f : expf(mw - top);
+                    lsum = fmaf(splits > 1 ? ws_ld_cluster(st + 1, ss) : st[1], f, lsum);
+                    a = fmaf(splits > 1 ? ws_ld_cluster(st + 2 + jv, ss) : st[2 + jv], f, a);
+                }
+            const int h = g * hg + hh;
+            const float gt = (gate ? wa_sigmoid(gate[(size_t)r * gate_ld + h]) : 1.0f) * out_scale;
+            orow[e] = prb_from_float<O>(lsum > 0.0f ? a / lsum * gt : 0.0f);
         }
-        const int h = g * hg + hh;
-        const float gt = (gate ? wa_sigmoid(gate[(size_t)r * gate_ld + h]) : 1.0f) * out_scale;
-        orow[e] = prb_from_float<O>(lsum > 0.0f ? a / lsum * gt : 0.0f);
     }
+    if (splits > 1) ws_cluster_sync();               // the states have been read: CTAs may leave
 }
 
 size_t ws_smem(int hg, int dim, int vdim, int nw) {
@@ -773,16 +801,36 @@ PRB_API int prb_wattn_single(void* out, long out_ld, const float* q, const void*
         return PRB_E_SIZE;
     const int hg = heads / kv_heads;
     const size_t smem = ws_smem(hg, dim, vdim, nw);
-    dim3 grid(n_tokens, kv_heads);
+    // CTAs a (token, key/value head): doubled while the step leaves half of the SMs idle and a
+    // request's keys (at most the window's and the kept ones) still give every CTA a round
+    long long most = (long long)max_pages * page_size;
+    if (window > 0 && (long long)window + keep_first + WT_KB < most) most = (long long)window + keep_first + WT_KB;
+    const long long rounds = (most + nw * WT_KB - 1) / (nw * WT_KB);
+    int splits = 1;
+    while (splits < 8 && splits * 2 <= rounds &&
+           (long long)n_tokens * kv_heads * splits * 2 <= prb_sm_count())
+        splits *= 2;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(n_tokens, kv_heads, splits);
+    cfg.blockDim = dim3(nw * 32);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = (unsigned)splits;
+    cfg.attrs = attr;
+    cfg.numAttrs = splits > 1 ? 1 : 0;
 #define WS2(CT, OT, VCN, PN)                                                                     \
     do {                                                                                         \
         if (smem > 48 * 1024)                                                                    \
             cudaFuncSetAttribute(wattn_single_kernel<CT, OT, VCN, PN>,                           \
                                  cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);        \
-        wattn_single_kernel<CT, OT, VCN, PN><<<grid, nw * 32, smem, stream>>>(                   \
-            (OT*)out, out_ld, q, (const CT*)cache, block_table, seq_of_token, positions, gate,   \
-            gate_ld, slopes, n_tokens, heads, kv_heads, dim, vdim, page_size, max_pages,         \
-            num_pages, window, keep_first, scale, out_scale, status);                            \
+        cudaLaunchKernelEx(&cfg, wattn_single_kernel<CT, OT, VCN, PN>, (OT*)out, out_ld, q,      \
+                           (const CT*)cache, block_table, seq_of_token, positions, gate,         \
+                           gate_ld, slopes, n_tokens, heads, kv_heads, dim, vdim, page_size,     \
+                           max_pages, num_pages, window, keep_first, scale, out_scale, status);  \
     } while (0)
 #define WS1(CT, OT, VCN)                                                                         \
     do {                                                                                         \

@@ -135,8 +135,10 @@ class PostNormGatedBlock(Block):
 class ParallelBlock(Block):
     """x <- x + (mixer(norm_1(x)) + feed_forward(norm_2(x))): both branches read the stream as
     it was before the layer, each through a norm of its own, and their results join it in
-    32-bit.  Both norms run before either branch adds to the stream.  A layer without a
-    feed-forward has the mixer's norm alone."""
+    32-bit.  The mixer's norm runs first; the feed-forward then reads the untouched stream
+    (its norm may ride in its first matrix product, see :class:`LazyNorm`) and adds its
+    result, and the mixer, which works from its normed copy, adds its own after that.  A
+    layer without a feed-forward has the mixer's norm alone."""
     graph_safe = True
 
     def __init__(self, mixer: Mixer, feed_forward: FeedForward, norms: Dict[str, Norm],
@@ -156,10 +158,9 @@ class ParallelBlock(Block):
         self.norms["mixer"].forward(ctx, x, h1)
         if self.has_ff:
             h2 = ctx.scratch("block_normed_2", (cap, self.width), self.runtime.dtype)[:t]
-            self.norms["feed_forward"].forward(ctx, x, h2)
+            self.feed_forward.forward(
+                ctx, PreNormBlock._normed(ctx, self.feed_forward, self.norms["feed_forward"], x, h2), x)
         self.mixer.forward(ctx, h1, x, cache)
-        if self.has_ff:
-            self.feed_forward.forward(ctx, h2, x)
 
 
 register_part("arrangement", "pre_norm", PreNormBlock)

@@ -59,6 +59,7 @@ class GatedMLP(FeedForward):
     (:meth:`fuse_input_rows`); its float32 result feeds the activation unrounded."""
     graph_safe = True
     can_overwrite = True
+    accepts_lazy_norm = True      # the first matrix product may compute the norm itself
 
     def __init__(self, gate, up, down, width: int, inner: int, limit: float, act_alpha: float,
                  up_shift: float, runtime):
@@ -105,6 +106,7 @@ class GatedMoE(FeedForward):
     pays for every expert's arithmetic: right for any sizes, cheap while experts are small."""
     graph_safe = True
     can_overwrite = True
+    accepts_lazy_norm = True      # the first matrix product may compute the norm itself
 
     def __init__(self, p: dict, store, runtime):
         from .latent_attention import FusedInput

@@ -18,10 +18,13 @@ Per head, over a 32-bit state S [dim, vdim] that starts at zero,
 (the bonus u acts on the current token only); each head's o is brought to unit root-mean-square,
 multiplied by a weight per channel and by the gate, and projected.  The state and the last
 input row are per-request STATE of the cache manager (a slot per live request), so a prompt may
-be cut anywhere and decoding is the same kernels with one token.  The five projections write
-column ranges of one 32-bit buffer that feeds the recurrence unrounded; decays, their
-exponentials, the state and the unit norm are 32-bit.  Sizes, eps and the constant on the
-result are parameters.
+be cut anywhere and decoding is the same kernels with one token.  A projection of a blend is
+linear in it, M b_s = M x_t + (M diag(mu_s)) (x_(t-1) - x_t): the five projections are ONE
+product of the pair [x_t | x_(t-1) - x_t] with the rows [M | M diag(mu_s)] of all five (the
+blend weights are folded into the matrices when the model is built), whose 32-bit result feeds
+the recurrence unrounded; decays, their exponentials, the state and the unit norm are 32-bit.
+Steps of few tokens run the recurrence with the finish in one launch; longer portions are cut
+into segments that run side by side.  Sizes, eps and the constant on the result are parameters.
 """
 from __future__ import annotations
 
@@ -29,7 +32,8 @@ import torch
 
 from ..csrc import ops
 from .interfaces import LayerCache, Mixer, StateSpec
-from .linear import Linear, padded_linear
+from .latent_attention import FusedInput
+from .linear import padded_linear
 from .registry import register_part
 
 _BLENDS = ("r", "k", "v", "g", "w")
@@ -65,19 +69,17 @@ class TimeMix(Mixer):
         if w1.dim() != 2 or w1.shape[1] != self.width:
             raise ValueError(f"{w['w1']}: expected [rank, {self.width}], found {list(w1.shape)}")
         self.rank = int(w1.shape[0])
-        # the five products write column ranges (at multiples of 8) of one 32-bit buffer
+        # one product for the five projections: rows [M | M diag(mu_s)] against [x | x' - x]
         mats = {"r": need("r", (hk, self.width)), "k": need("k", (hk, self.width)),
                 "v": need("v", (hv, self.width)), "g": need("g", (hv, self.width)), "w": w1}
-        self.linear, self.cols, at = {}, {}, 0
-        for s in _BLENDS:
-            self.linear[s] = Linear(mats[s], None, runtime)
-            self.cols[s] = (at, mats[s].shape[0])
-            at += _pad8(mats[s].shape[0])
-        self.cols["decay"] = (at, hk)                # the segmented scan leaves the decays here
-        self.proj_width = at + _pad8(hk)
-        self.one_launch = torch.cuda.is_available() and ops.tmix_step_supports(self.dim, self.vdim)
         f32 = lambda t: t.to(torch.float32).contiguous()
-        self.mu = torch.stack([f32(need("mu_" + s, (self.width,))) for s in _BLENDS]).contiguous()
+        self.input = FusedInput(2 * self.width, runtime, "tmix_proj")
+        for s in _BLENDS:
+            m, mu = f32(mats[s]), f32(need("mu_" + s, (self.width,)))
+            self.input.add(s, torch.cat([m, m * mu[None, :]], dim=1))
+        self.input.linear()
+        self.cols = self.input.cols
+        self.one_launch = torch.cuda.is_available() and ops.tmix_step_supports(self.dim, self.vdim)
         self.w2 = f32(need("w2", (hk, self.rank)))
         self.w0 = f32(need("w0", (hk,)))
         self.u = f32(need("u", (self.heads, self.dim)))
@@ -92,14 +94,10 @@ class TimeMix(Mixer):
         t = x.shape[0]
         cap = ctx.token_capacity
         state, prev = cache.state["time_mix"], cache.state["time_mix_input"]
-        blends = ctx.scratch("tmix_blends", (cap, len(_BLENDS) * self.width), self.runtime.dtype)[:t]
-        ops.tmix_shift(blends, h, prev, self.mu, ctx.seq_of_token, ctx.positions, ctx.q_start,
+        pair = ctx.scratch("tmix_pair", (cap, 2 * self.width), self.runtime.dtype)[:t]
+        ops.tmix_shift(pair, h, prev, None, ctx.seq_of_token, ctx.positions, ctx.q_start,
                        ctx.state_slot, ctx.status)
-        proj = ctx.scratch("tmix_proj", (cap, self.proj_width), torch.float32)[:t]
-        for i, s in enumerate(_BLENDS):
-            at, n = self.cols[s]
-            self.linear[s].forward(ctx, blends[:, i * self.width:(i + 1) * self.width],
-                                   proj[:, at:at + n])
+        proj = self.input.run(ctx, pair)
         raw = ctx.scratch("tmix_raw", (cap, self.heads * self.vdim), torch.float32)[:t]
         gated = ctx.scratch_zero("tmix_gated", (cap, self.out.n_in), self.runtime.dtype)[:t]
         requests = ctx.layout.b_cap
@@ -124,7 +122,7 @@ class TimeMix(Mixer):
             scan(segments=(ctx.scratch("tmix_seg_own", shape, torch.float32),
                            ctx.scratch("tmix_seg_start", shape, torch.float32),
                            ctx.scratch("tmix_seg_decay", (n, self.heads, self.dim), torch.float32)),
-                 w_col=self.cols["decay"][0])
+                 decays=ctx.scratch("tmix_decays", (cap, self.heads * self.dim), torch.float32)[:t])
         ops.tmix_finish(gated, raw, proj, self.cols["g"][0], self.norm, ctx.seq_of_token,
                         self.heads, self.vdim, self.eps, self.out_scale)
         self.out.forward(ctx, gated, x, resid=x if accumulate else None)

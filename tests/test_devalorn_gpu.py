@@ -88,8 +88,7 @@ class TimeMixCase:
             n = r.shape[0]
             pad = torch.zeros(n, 4)
             proj.append(torch.cat([pad, r.reshape(n, -1), k.reshape(n, -1), pad, v.reshape(n, -1),
-                                   gate.reshape(n, -1), pad, lr, pad, torch.full((n, hd * d), 77.0),
-                                   pad], dim=1))
+                                   gate.reshape(n, -1), pad, lr], dim=1))
             hs.append(h)
             pos += list(range(p0, p0 + n))
             seq += [b] * n
@@ -102,7 +101,6 @@ class TimeMixCase:
         v_col = 8 + 2 * hd * d
         g_col = v_col + hd * vd
         lr_col = g_col + hd * vd + 4
-        w_col = lr_col + rk + 4
         raw = torch.empty(t, hd * vd, device=DEV)
         status = torch.zeros(4, dtype=torch.int32, device=DEV)
         out = torch.zeros(t, hd * vd + 8, dtype=out_dtype, device=DEV)
@@ -113,7 +111,8 @@ class TimeMixCase:
             n = ops.tmix_max_segments(t, len(parts) + 1) + 2
             extra = {"segments": (torch.full((n, hd, vd, d), 3.0, device=DEV),
                                   torch.full((n, hd, vd, d), 3.0, device=DEV),
-                                  torch.full((n, hd, d), 3.0, device=DEV)), "w_col": w_col}
+                                  torch.full((n, hd, d), 3.0, device=DEV)),
+                     "decays": torch.full((t + 2, hd * d + 8), 77.0, device=DEV)[:t]}
         elif mode == "step":
             extra = {"finish": (out, g_col, self.norm_w.to(DEV), eps, scale)}
         ops.tmix_scan(raw, proj, r_col, k_col, v_col, lr_col, self.w2.to(DEV), self.w0.to(DEV),
@@ -233,6 +232,24 @@ def test_time_mix_shift_kernel():
                 assert torch.allclose(out[lo:hi, s * width:(s + 1) * width].cpu().double(), want, atol=tol, rtol=tol)
         assert float(out[11, :n_mix * width].float().abs().max()) == 0.0
         assert float((out[:, n_mix * width:].float() - 7.0).abs().max()) == 0.0
+        # without blend weights: the row beside its difference from the row before; a blend's
+        # projection is that pair's, M b_s = [M | M diag(mu_s)] [h | h' - h]
+        pair = torch.full((12, 2 * width + 8), 7.0, dtype=dtype, device=DEV)
+        ops.tmix_shift(pair, h.to(dtype).to(DEV), prev.to(dtype).to(DEV), None, _i32(seq), _i32(pos),
+                       _i32([0, 5, 8, 9, 11]), _i32(slots), status)
+        assert int(status[0]) == 0
+        got = pair.cpu().double()
+        M = torch.randn(6, width, generator=g).double()
+        for (lo, hi), first in (((0, 5), None), ((5, 8), pp[0]), ((8, 9), pp[3]), ((9, 11), None)):
+            before = torch.cat([(torch.zeros(width).double() if first is None else first)[None], hh[lo:hi - 1]])
+            assert torch.equal(got[lo:hi, :width], hh[lo:hi])
+            assert torch.allclose(got[lo:hi, width:2 * width], before - hh[lo:hi], atol=tol, rtol=tol)
+            for s in range(n_mix):
+                folded = torch.cat([M, M * mu[s].double()[None]], dim=1)
+                want = P.shifted_blend(hh[lo:hi], mu[s].double(), first) @ M.T
+                assert torch.allclose(got[lo:hi, :2 * width] @ folded.T, want, atol=20 * tol, rtol=20 * tol)
+        assert float(got[11, :2 * width].abs().max()) == 0.0
+        assert float((got[:, 2 * width:] - 7.0).abs().max()) == 0.0
 
 
 class WindowCase:
@@ -333,6 +350,27 @@ def test_window_attention_kernels(dtype, window, keep_first):
                      {"slopes": slopes * 40, "gate": gate}):
             got, want = case.run(queries, heads, window, keep_first, 0.3, tile_rows=tile_rows, **opts)
             assert torch.allclose(got, want, atol=tol, rtol=tol), (tile_rows, sorted(opts))
+
+
+@pytest.mark.parametrize("window,keep_first", [(0, 0), (600, 40), (100, 300)])
+@pytest.mark.parametrize("n_queries", [1, 3, 9, 30])
+def test_window_attention_few_single_tokens(window, keep_first, n_queries):
+    """Steps of so few single tokens that the single-token kernel splits a token's keys over
+    several CTAs: every number of CTAs a token, some of them without a key block of their own."""
+    heads, kv_heads, dim, vdim = 6, 2, 32, 64
+    lengths = [900, 40, 300]
+    case = WindowCase(lengths, kv_heads, dim, vdim, torch.bfloat16, seed=11)
+    g = torch.Generator().manual_seed(3)
+    places = [(0, 899), (1, 39), (2, 299), (0, 0), (0, 31), (0, 32), (0, 255), (0, 256), (0, 600)]
+    places = (places * 4)[:n_queries]
+    queries = [(b, p, torch.randn(heads, dim, generator=g)) for b, p in places]
+    slopes = P.distance_slopes(heads, torch.float64)
+    gate = torch.randn(len(queries), heads, generator=g)
+    got, want = case.run(queries, heads, window, keep_first, 0.2, slopes=slopes, gate=gate, tile_rows=-1)
+    assert torch.allclose(got, want, atol=2e-2, rtol=2e-2)
+    case32 = WindowCase(lengths, kv_heads, dim, vdim, torch.float32, seed=11)
+    got, want = case32.run(queries, heads, window, keep_first, 0.2, slopes=slopes, gate=gate, tile_rows=-1)
+    assert torch.allclose(got, want, atol=2e-5, rtol=2e-5)
 
 
 @pytest.mark.parametrize("heads,kv_heads,dim,vdim", [(1, 1, 8, 136), (8, 1, 16, 8), (3, 3, 80, 24),
