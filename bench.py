@@ -151,6 +151,9 @@ def main() -> int:
                     help="the decode attention kernel alone, by split size")
     ap.add_argument("--profile-latent", default=None, metavar="HEADS,RANK,ROT,ITEMS,CONTEXT[,TOKENS]",
                     help="the tensor-core attention over shared latent rows alone, by key range")
+    ap.add_argument("--profile-design", default=None, metavar="NAME[,LAYERS[,REQUESTS[,CONTEXT]]]",
+                    help="a named size of any design cut to its first layers: a few prompt and "
+                         "decode steps, kernels launched one by one (for profiler captures)")
     ap.add_argument("--profile-sample", default=None, metavar="ROWS,VOCAB,K",
                     help="the sampling kernel alone")
     ap.add_argument("--kernel-table", action="store_true",
@@ -197,6 +200,8 @@ def main() -> int:
         return profiles.profile_attention(args.profile_attention)
     if args.profile_decode_attention:
         return profiles.profile_decode_attention(args.profile_decode_attention)
+    if args.profile_design:
+        return profiles.profile_design(args.profile_design)
     if args.profile_sample:
         return profiles.profile_sample(args.profile_sample)
     if args.profile_latent:

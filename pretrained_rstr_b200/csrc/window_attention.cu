@@ -533,7 +533,7 @@ wattn_single_kernel(O* __restrict__ out, long out_ld, const float* __restrict__ 
         constexpr int VE = 16 / (int)sizeof(C);
         if (rowlen % VE == 0 && dim % VE == 0) {
             const int nv = rowlen / VE;
-#pragma unroll 4
+#pragma unroll 8
             for (int e = threadIdx.x; e < keys * nv; e += blockDim.x) {
                 const int kk = e / nv, vi = e - kk * nv;
                 const long long row = rows_s[kk];
@@ -801,15 +801,15 @@ PRB_API int prb_wattn_single(void* out, long out_ld, const float* q, const void*
         return PRB_E_SIZE;
     const int hg = heads / kv_heads;
     const size_t smem = ws_smem(hg, dim, vdim, nw);
-    // CTAs a (token, key/value head): doubled while the step leaves half of the SMs idle and a
-    // request's keys (at most the window's and the kept ones) still give every CTA a round
+    // CTAs a (token, key/value head): as many as the SMs the step would leave idle allow, while
+    // a request's keys (at most the window's and the kept ones) still give every CTA a round
     long long most = (long long)max_pages * page_size;
     if (window > 0 && (long long)window + keep_first + WT_KB < most) most = (long long)window + keep_first + WT_KB;
     const long long rounds = (most + nw * WT_KB - 1) / (nw * WT_KB);
     int splits = 1;
-    while (splits < 8 && splits * 2 <= rounds &&
-           (long long)n_tokens * kv_heads * splits * 2 <= prb_sm_count())
-        splits *= 2;
+    while (splits < 8 && splits + 1 <= rounds &&
+           (long long)n_tokens * kv_heads * (splits + 1) <= prb_sm_count())
+        ++splits;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(n_tokens, kv_heads, splits);
     cfg.blockDim = dim3(nw * 32);

@@ -76,6 +76,25 @@ def cache_bytes_per_token(m) -> int:
                for g in m.loaded.model.group_specs)
 
 
+def _mixers(m):
+    """Every mixer of the model's layer runs (the two of a pair side by side apart)."""
+    for block in m.loaded.model.blocks:
+        mixer = getattr(block, "mixer", None)
+        if mixer is not None:
+            yield from getattr(mixer, "children", [mixer])
+
+
+def request_bytes(m, context: int) -> int:
+    """Bytes a decode step reads (and, for running states, writes back) for ONE request that
+    holds ``context`` tokens: mixers that say so themselves (``step_bytes(context)``: a window's
+    keys, a layer that reads another's cache, a state) are asked; the others count every cache
+    row of the context."""
+    asked = [mx.step_bytes(context) for mx in _mixers(m) if hasattr(mx, "step_bytes")]
+    if asked:
+        return sum(asked)
+    return context * cache_bytes_per_token(m)
+
+
 def measure_size(name: str, batches: Sequence[int] = (1, 8, 64), context: int = 1000,
                  steps: int = 32, warmup: int = 4, layers: Optional[int] = None) -> Dict:
     m, raw = load_size(name, layers)
@@ -83,7 +102,8 @@ def measure_size(name: str, batches: Sequence[int] = (1, 8, 64), context: int = 
     vocab = m.loaded.model.vocab
     wbytes, kvb, mflops = weight_bytes(m), cache_bytes_per_token(m), matrix_flops_per_token(m)
     out = {"layers": len(m.loaded.model.blocks), "weight_mb": round(wbytes / 1e6, 1),
-           "cache_bytes_per_token": kvb, "matrix_gflop_per_token": round(mflops / 1e9, 4)}
+           "cache_bytes_per_token": kvb, "request_bytes_at_context": request_bytes(m, context),
+           "matrix_gflop_per_token": round(mflops / 1e9, 4)}
     pre = statistics.median(timed_prefill(m.loaded, 2, 1024, vocab))
     out["prefill_2x1024"] = {"ms": round(pre, 4), "tokens_per_s": round(2048 / (pre / 1e3)),
                              "matrix_frac_of_bf16_peak": round(
@@ -91,7 +111,7 @@ def measure_size(name: str, batches: Sequence[int] = (1, 8, 64), context: int = 
     for b in batches:
         res = timed_decode(m.engine, b, context, steps, warmup, vocab, 1000 * b + context)
         ms = statistics.mean(res["ms"])
-        nbytes = wbytes + b * res["mean_context"] * kvb
+        nbytes = wbytes + b * request_bytes(m, int(res["mean_context"]))
         out[f"decode_b{b}"] = {"ms": round(ms, 4), "tokens_per_s": round(b / (ms / 1e3)),
                                "e2e_tokens_per_s": round(b * steps / res["wall_s"]),
                                "launches_per_step": round(res["launches"] / steps, 1),

@@ -443,6 +443,48 @@ def profile_decode_attention(spec: str) -> int:
     return 0
 
 
+def profile_design(spec: str) -> int:
+    """NAME[,LAYERS[,REQUESTS[,CONTEXT]]]: a named size of any design cut to its first LAYERS
+    layers (default 2), kernels launched one by one: REQUESTS (8) prompts of CONTEXT (900)
+    tokens, two to a step, then three steps of single tokens.  For profiler captures (no
+    graphs, no torch profiler); prints the device time of a prompt step and a decode step."""
+    import random
+    import torch
+    from pretrained_rstr_b200.engine.batch import Entry
+    from .designs import load_size
+    parts = spec.split(",")
+    name = parts[0]
+    layers, requests, context = [int(v) for v in parts[1:4]] + [2, 8, 900][len(parts) - 1:]
+    m, _raw = load_size(name, layers, max_lanes=max(8, requests), maxpos=context + 64)
+    runner, cache = m.loaded.runner, m.loaded.cache
+    runner.use_graphs = False
+    vocab = m.loaded.model.vocab
+    rng = random.Random(0)
+
+    def timed(entries):
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        start.record()
+        runner.step(entries)
+        end.record()
+        torch.cuda.synchronize()
+        return start.elapsed_time(end)
+
+    rids = [("p", i) for i in range(requests)]
+    for rid in rids:
+        cache.open(rid)
+    prompt_ms = [timed([Entry(rid, [rng.randrange(vocab) for _ in range(context)], [context - 1])
+                        for rid in rids[i:i + 2]]) for i in range(0, requests, 2)]
+    decode_ms = [timed([Entry(rid, [rng.randrange(vocab)], [0]) for rid in rids]) for _ in range(3)]
+    runner.check_status()
+    for rid in rids:
+        cache.close(rid)
+    print(json.dumps({"profile_design": spec, "layers": layers,
+                      "prompt_step_ms": [round(t, 3) for t in prompt_ms],
+                      "decode_step_ms": [round(t, 3) for t in decode_ms]}))
+    return 0
+
+
 def profile_sample(spec: str) -> int:
     """The sampling kernel alone: ROWS rows of VOCAB float32 logits, top-k K ("ROWS,VOCAB,K"):
     greedy, and temperature 0.8 with top-p 1.0 and 0.9."""

@@ -90,6 +90,10 @@ class TimeMix(Mixer):
         return [StateSpec("time_mix", (self.heads, self.vdim, self.dim), torch.float32),
                 StateSpec("time_mix_input", (self.width,), self.runtime.dtype)]
 
+    def step_bytes(self, context: int) -> int:
+        """State bytes a single token reads and writes back, whatever the context."""
+        return 2 * (self.heads * self.vdim * self.dim * 4 + self.width * self.runtime.dtype.itemsize)
+
     def forward(self, ctx, h, x, cache: LayerCache, accumulate: bool = True) -> None:
         t = x.shape[0]
         cap = ctx.token_capacity

@@ -99,6 +99,11 @@ class WindowAttention(Mixer):
     def kv_spec(self) -> KVSpec:
         return KVSpec(self.kv_heads, self.dim + self.vdim, None, values=False)
 
+    def step_bytes(self, context: int) -> int:
+        """Cache bytes a single token at ``context`` tokens reads: the rows it sees."""
+        seen = min(context, self.window + self.keep_first) if self.window else context
+        return seen * self.kv_heads * (self.dim + self.vdim) * self.runtime.dtype.itemsize
+
     def fuse_input_rows(self, name: str, weight) -> str:
         return self.input.add(name, weight)
 
