@@ -454,6 +454,25 @@ __device__ __forceinline__ float ws_ld_cluster(const float* local, int rank) {
     return v;
 }
 
+// A staged key row holds the cache's own numbers (bfloat16 rows are half the size of 32-bit
+// ones: twice the keys a round, or several CTAs an SM); its pitch is an odd number of 4-byte
+// words, so that the lanes, a key each, read their rows without bank conflicts.
+template <typename C>
+__device__ __forceinline__ void ws_k4(const uint32_t* krow, int d, float& a0, float& a1, float& a2, float& a3);
+template <>
+__device__ __forceinline__ void ws_k4<float>(const uint32_t* krow, int d, float& a0, float& a1, float& a2, float& a3) {
+    const float* f = reinterpret_cast<const float*>(krow);
+    a0 = f[d]; a1 = f[d + 1]; a2 = f[d + 2]; a3 = f[d + 3];
+}
+template <>
+__device__ __forceinline__ void ws_k4<__nv_bfloat16>(const uint32_t* krow, int d, float& a0, float& a1, float& a2, float& a3) {
+    const uint32_t w0 = krow[d >> 1], w1 = krow[(d >> 1) + 1];       // (a bfloat16 is a float's upper half)
+    a0 = __uint_as_float(w0 << 16); a1 = __uint_as_float(w0 & 0xffff0000u);
+    a2 = __uint_as_float(w1 << 16); a3 = __uint_as_float(w1 & 0xffff0000u);
+}
+__host__ __device__ inline int ws_kwords(int dim, int csize) { return ((dim * csize + 3) / 4) | 1; }
+__host__ __device__ inline int ws_vbytes(int vdim, int csize) { return (vdim * csize + 15) / 16 * 16; }
+
 template <typename C, typename O, int VC, int PPW>
 __global__ void __launch_bounds__(WT_WARPS * 32)
 wattn_single_kernel(O* __restrict__ out, long out_ld, const float* __restrict__ q,
@@ -470,14 +489,15 @@ wattn_single_kernel(O* __restrict__ out, long out_ld, const float* __restrict__ 
     const int hg = heads / kv_heads;
     const int g = blockIdx.y, r = blockIdx.x;
     const int rowlen = dim + vdim;
-    const int kpitch = dim + 1;                      // odd: lanes read their own key's row
     const int qpitch = (dim + 3) / 4 * 4;
     const int keys = nw * WT_KB;
     const int jpitch = 2 + vdim;
-    float* Ks = smem;                                // [keys][kpitch]
-    float* Vs = Ks + (keys * kpitch + 3) / 4 * 4;    // [keys][vdim]
-    float* Qs = Vs + (keys * vdim + 3) / 4 * 4;      // [hg][qpitch]
+    const int pw = ws_kwords(dim, (int)sizeof(C));   // a staged key's pitch in 4-byte words (odd)
+    const int vpb = ws_vbytes(vdim, (int)sizeof(C)); // a staged value row's pitch in bytes
+    float* Qs = smem;                                // [hg][qpitch]
     float* Js = Qs + hg * qpitch;                    // [nw][hg][2 + vdim]
+    uint32_t* Kw = reinterpret_cast<uint32_t*>(Js + (nw * hg * jpitch + 3) / 4 * 4);   // [keys][pw]
+    unsigned char* Vb = reinterpret_cast<unsigned char*>(Kw + (keys * pw + 3) / 4 * 4); // [keys][vpb]
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     O* orow = out + (size_t)r * out_ld + (size_t)g * hg * vdim;
     const int b = seq_of_token[r];
@@ -539,19 +559,21 @@ wattn_single_kernel(O* __restrict__ out, long out_ld, const float* __restrict__ 
                 const long long row = rows_s[kk];
                 uint4 raw = make_uint4(0u, 0u, 0u, 0u);
                 if (row >= 0) raw = *reinterpret_cast<const uint4*>(cache + (size_t)row * rowlen + vi * VE);
-                const C* vals = reinterpret_cast<const C*>(&raw);
                 const int off = vi * VE;
-                float* dst = off < dim ? Ks + kk * kpitch + off : Vs + kk * vdim + off - dim;
-#pragma unroll
-                for (int x = 0; x < VE; ++x) dst[x] = prb_to_float<C>(vals[x]);
+                if (off < dim) {                     // (the odd pitch: word by word)
+                    uint32_t* dst = Kw + kk * pw + off * (int)sizeof(C) / 4;
+                    dst[0] = raw.x; dst[1] = raw.y; dst[2] = raw.z; dst[3] = raw.w;
+                } else {
+                    *reinterpret_cast<uint4*>(Vb + (size_t)kk * vpb + (size_t)(off - dim) * sizeof(C)) = raw;
+                }
             }
         } else {
             for (int e = threadIdx.x; e < keys * rowlen; e += blockDim.x) {
                 const int kk = e / rowlen, off = e - kk * rowlen;
                 const long long row = rows_s[kk];
-                const float val = row < 0 ? 0.0f : prb_to_float<C>(cache[(size_t)row * rowlen + off]);
-                if (off < dim) Ks[kk * kpitch + off] = val;
-                else Vs[kk * vdim + off - dim] = val;
+                const C val = row < 0 ? prb_from_float<C>(0.0f) : cache[(size_t)row * rowlen + off];
+                if (off < dim) reinterpret_cast<C*>(Kw + kk * pw)[off] = val;
+                else reinterpret_cast<C*>(Vb + (size_t)kk * vpb)[off - dim] = val;
             }
         }
         __syncthreads();
@@ -562,14 +584,15 @@ wattn_single_kernel(O* __restrict__ out, long out_ld, const float* __restrict__ 
         const int k_hi = min(min(WT_KB, j_end - j0), p - j0 + 1);
         if (k_hi <= 0) continue;
         const int j = j0 + lane;
-        const float* krow = Ks + (warp * WT_KB + lane) * kpitch;
-        const float* vblk = Vs + (size_t)warp * WT_KB * vdim;
+        const uint32_t* krow = Kw + (warp * WT_KB + lane) * pw;
+        const unsigned char* vblk = Vb + (size_t)warp * WT_KB * vpb;
         float s[PPW];
 #pragma unroll
         for (int x = 0; x < PPW; ++x) s[x] = 0.0f;
         if (dim % 4 == 0) {
             for (int d = 0; d < dim; d += 4) {
-                const float a0 = krow[d], a1 = krow[d + 1], a2 = krow[d + 2], a3 = krow[d + 3];
+                float a0, a1, a2, a3;
+                ws_k4<C>(krow, d, a0, a1, a2, a3);
 #pragma unroll
                 for (int x = 0; x < PPW; ++x) {
                     if (x < hg) {
@@ -580,7 +603,7 @@ wattn_single_kernel(O* __restrict__ out, long out_ld, const float* __restrict__ 
             }
         } else {
             for (int d = 0; d < dim; ++d) {
-                const float a0 = krow[d];
+                const float a0 = prb_to_float<C>(reinterpret_cast<const C*>(krow)[d]);
 #pragma unroll
                 for (int x = 0; x < PPW; ++x)
                     if (x < hg) s[x] = fmaf(Qs[x * qpitch + d], a0, s[x]);
@@ -605,7 +628,9 @@ wattn_single_kernel(O* __restrict__ out, long out_ld, const float* __restrict__ 
         for (int kk = 0; kk < k_hi; ++kk) {
             float v[VC];
 #pragma unroll
-            for (int c = 0; c < VC; ++c) v[c] = (lane + 32 * c < vdim) ? vblk[kk * vdim + lane + 32 * c] : 0.0f;
+            for (int c = 0; c < VC; ++c)
+                v[c] = (lane + 32 * c < vdim)
+                    ? prb_to_float<C>(reinterpret_cast<const C*>(vblk + (size_t)kk * vpb)[lane + 32 * c]) : 0.0f;
 #pragma unroll
             for (int x = 0; x < PPW; ++x) {
                 const float w = __shfl_sync(0xffffffffu, e[x], kk);
@@ -655,19 +680,20 @@ wattn_single_kernel(O* __restrict__ out, long out_ld, const float* __restrict__ 
     if (splits > 1) ws_cluster_sync();               // the states have been read: CTAs may leave
 }
 
-size_t ws_smem(int hg, int dim, int vdim, int nw) {
+size_t ws_smem(int hg, int dim, int vdim, int nw, int csize) {
     const int keys = nw * WT_KB;
-    return (size_t)((keys * (dim + 1) + 3) / 4 * 4 + (keys * vdim + 3) / 4 * 4 +
-                    hg * ((dim + 3) / 4 * 4) + nw * hg * (2 + vdim)) * sizeof(float);
+    return (size_t)(hg * ((dim + 3) / 4 * 4) + (nw * hg * (2 + vdim) + 3) / 4 * 4 +
+                    (keys * ws_kwords(dim, csize) + 3) / 4 * 4) * 4 + (size_t)keys * ws_vbytes(vdim, csize);
 }
 
-// Warps (key blocks a round) of the single-token kernel for these sizes; 0: it does not take them.
-int ws_warps(int heads, int kv_heads, int dim, int vdim) {
+// Warps (key blocks a round) of the single-token kernel for these sizes and a cache of `csize`
+// bytes a number; 0: it does not take them.
+int ws_warps(int heads, int kv_heads, int dim, int vdim, int csize) {
     if (heads <= 0 || kv_heads <= 0 || heads % kv_heads != 0) return 0;
     const int hg = heads / kv_heads;
     if (hg > WS_MAX_PPW || vdim > 32 * WT_VC || dim > 512) return 0;
     for (int nw = WT_WARPS; nw >= 1; nw >>= 1)
-        if (ws_smem(hg, dim, vdim, nw) <= 200 * 1024) return nw;
+        if (ws_smem(hg, dim, vdim, nw, csize) <= 200 * 1024) return nw;
     return 0;
 }
 
@@ -784,7 +810,7 @@ PRB_API int prb_wattn_tile(void* out, long out_ld, const float* q, const void* c
 
 // 1 if the single-token kernel takes these sizes.
 PRB_API int prb_wattn_single_supports(int heads, int kv_heads, int dim, int vdim) {
-    return ws_warps(heads, kv_heads, dim, vdim) > 0 ? 1 : 0;
+    return ws_warps(heads, kv_heads, dim, vdim, 4) > 0 ? 1 : 0;     // (a 32-bit cache is the larger)
 }
 
 PRB_API int prb_wattn_single(void* out, long out_ld, const float* q, const void* cache,
@@ -795,12 +821,14 @@ PRB_API int prb_wattn_single(void* out, long out_ld, const float* q, const void*
                              float out_scale, int cache_dtype, int out_dtype, int* status,
                              cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
-    const int nw = ws_warps(heads, kv_heads, dim, vdim);
+    if (cache_dtype != PRB_F32 && cache_dtype != PRB_BF16) return PRB_E_DTYPE;
+    const int csize = cache_dtype == PRB_F32 ? 4 : 2;
+    const int nw = ws_warps(heads, kv_heads, dim, vdim, csize);
     if (nw <= 0 || kv_heads > 65535 || page_size <= 0 || max_pages <= 0 || window < 0 ||
         keep_first < 0)
         return PRB_E_SIZE;
     const int hg = heads / kv_heads;
-    const size_t smem = ws_smem(hg, dim, vdim, nw);
+    const size_t smem = ws_smem(hg, dim, vdim, nw, csize);
     // CTAs a (token, key/value head): as many as the SMs the step would leave idle allow, while
     // a request's keys (at most the window's and the kept ones) still give every CTA a round
     long long most = (long long)max_pages * page_size;
