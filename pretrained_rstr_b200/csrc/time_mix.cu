@@ -255,19 +255,34 @@ __device__ __forceinline__ bool tm_find_segment(const int* q_start, int n_reques
     return false;
 }
 
-// A CTA per token: tanh of the low-rank row in shared memory, a thread per channel.
+// A CTA per TD_TOKENS tokens: their low-rank rows' tanh in shared memory; a thread per channel
+// holds nothing but walks its row of W2 once per token (the row stays in L1 for the CTA's tokens).
+constexpr int TD_TOKENS = 8;
 __global__ void tmix_decay_kernel(SegArgs a) {
-    extern __shared__ float th[];
+    extern __shared__ float th[];                    // [TD_TOKENS][rank]
     prb_grid_launch_dependents();
-    const int t = blockIdx.x;
-    const float* row = a.proj + (size_t)t * a.ld;
-    for (int j = threadIdx.x; j < a.rank; j += blockDim.x) th[j] = tanhf(row[a.lr_col + j]);
+    const int t0 = blockIdx.x * TD_TOKENS;
+    const int nt = min(TD_TOKENS, a.n_tokens - t0);
+    for (int e = threadIdx.x; e < nt * a.rank; e += blockDim.x) {
+        const int tt = e / a.rank, j = e - tt * a.rank;
+        th[e] = tanhf(a.proj[(size_t)(t0 + tt) * a.ld + a.lr_col + j]);
+    }
     __syncthreads();
     for (int ch = threadIdx.x; ch < a.heads * a.dim; ch += blockDim.x) {
         const float* wr = a.w2 + (size_t)ch * a.rank;
-        float z = a.w0[ch];
-        for (int j = 0; j < a.rank; ++j) z = fmaf(wr[j], th[j], z);
-        a.decay[(size_t)t * a.decay_ld + ch] = expf(-expf(z));
+        const float z0 = a.w0[ch];
+        float z[TD_TOKENS];
+#pragma unroll
+        for (int tt = 0; tt < TD_TOKENS; ++tt) z[tt] = z0;
+        for (int j = 0; j < a.rank; ++j) {
+            const float wj = wr[j];
+#pragma unroll
+            for (int tt = 0; tt < TD_TOKENS; ++tt)
+                if (tt < nt) z[tt] = fmaf(wj, th[tt * a.rank + j], z[tt]);
+        }
+#pragma unroll
+        for (int tt = 0; tt < TD_TOKENS; ++tt)
+            if (tt < nt) a.decay[(size_t)(t0 + tt) * a.decay_ld + ch] = expf(-expf(z[tt]));
     }
 }
 
@@ -563,7 +578,8 @@ PRB_API int prb_tmix_scan_segments(float* raw, long raw_ld, const float* proj, l
     SegArgs a{raw, raw_ld, proj, ld, r_col, k_col, v_col, lr_col, decay, decay_ld, w2, w0, u, state, h, h_ld,
               prev_state, q_start, state_slot, positions, n_tokens, n_requests, heads, dim, vdim,
               rank, width, lanes, cols, n_slots, seg_own, seg_start, seg_decay, status};
-    tmix_decay_kernel<<<n_tokens, 256, (size_t)rank * sizeof(float), stream>>>(a);
+    tmix_decay_kernel<<<(n_tokens + TD_TOKENS - 1) / TD_TOKENS, 256,
+                        (size_t)TD_TOKENS * rank * sizeof(float), stream>>>(a);
     PRB_LAUNCH_CHECK();
     const dim3 grid(heads, need, groups);
     const size_t per_head = (size_t)vdim * dim;

@@ -234,7 +234,7 @@ constexpr int WT_VC = 4;             // value coordinates a lane owns at most (v
 constexpr int WT_KB = 32;            // keys per block
 
 template <typename C, typename O, int VC>
-__global__ void __launch_bounds__(WT_WARPS * 32)
+__global__ void __launch_bounds__(WT_WARPS * 32, 2)
 wattn_tile_kernel(O* __restrict__ out, long out_ld, const float* __restrict__ q,
                   const C* __restrict__ cache, const int* __restrict__ block_table,
                   const int* __restrict__ seq_of_token, const int* __restrict__ positions,
@@ -253,6 +253,7 @@ wattn_tile_kernel(O* __restrict__ out, long out_ld, const float* __restrict__ q,
     float* Ks = smem;                                // [WT_KB][kpitch]
     float* Vs = Ks + (WT_KB * kpitch + 3) / 4 * 4;   // [WT_KB][vdim]
     float* Qs = Vs + (WT_KB * vdim + 3) / 4 * 4;     // [WT_WARPS * WT_PPW][qpitch]
+    float* Ps = Qs + WT_WARPS * WT_PPW * qpitch;     // [WT_WARPS][WT_KB][WT_PPW]: a block's weights
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int r_begin = blockIdx.x * tq;
     const int r_end = min(n_tokens, r_begin + tq);
@@ -400,15 +401,23 @@ wattn_tile_kernel(O* __restrict__ out, long out_ld, const float* __restrict__ q,
 #pragma unroll
                 for (int c = 0; c < VC; ++c) acc[x][c] *= f;
             }
+            // a key's weights for the warp's four pairs go through shared memory: one 16-byte
+            // load that all lanes share instead of four shuffles a key
+            static_assert(WT_PPW == 4, "a key's weights are one float4");
+            float* pw = Ps + (size_t)warp * WT_KB * WT_PPW;
+            __syncwarp();                            // the block before has been read
+            *reinterpret_cast<float4*>(pw + lane * WT_PPW) = make_float4(e[0], e[1], e[2], e[3]);
+            __syncwarp();
             for (int kk = 0; kk < k_hi; ++kk) {
                 float v[VC];
 #pragma unroll
                 for (int c = 0; c < VC; ++c) v[c] = (lane + 32 * c < vdim) ? Vs[kk * vdim + lane + 32 * c] : 0.0f;
+                const float4 w4 = *reinterpret_cast<const float4*>(pw + kk * WT_PPW);
+                const float w[WT_PPW] = {w4.x, w4.y, w4.z, w4.w};
 #pragma unroll
                 for (int x = 0; x < WT_PPW; ++x) {
-                    const float w = __shfl_sync(0xffffffffu, e[x], kk);
 #pragma unroll
-                    for (int c = 0; c < VC; ++c) acc[x][c] = fmaf(w, v[c], acc[x][c]);
+                    for (int c = 0; c < VC; ++c) acc[x][c] = fmaf(w[x], v[c], acc[x][c]);
                 }
             }
         }
@@ -699,7 +708,7 @@ int ws_warps(int heads, int kv_heads, int dim, int vdim, int csize) {
 
 size_t wt_smem(int dim, int vdim) {
     return (size_t)((WT_KB * (dim + 1) + 3) / 4 * 4 + (WT_KB * vdim + 3) / 4 * 4 +
-                    WT_WARPS * WT_PPW * ((dim + 3) / 4 * 4)) * sizeof(float);
+                    WT_WARPS * WT_PPW * ((dim + 3) / 4 * 4) + WT_WARPS * WT_KB * WT_PPW) * sizeof(float);
 }
 }  // namespace
 
