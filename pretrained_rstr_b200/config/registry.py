@@ -38,7 +38,8 @@ class Architecture:
 
 _REGISTRY: Dict[str, Architecture] = {}
 _BUNDLED = ("pretrained_rstr_b200.models.gpt2", "pretrained_rstr_b200.models.redisun",
-            "pretrained_rstr_b200.models.pezarax", "pretrained_rstr_b200.models.devalorn")
+            "pretrained_rstr_b200.models.pezarax", "pretrained_rstr_b200.models.devalorn",
+            "pretrained_rstr_b200.models.vakilorn")
 _bundled_loaded = False
 
 

@@ -2,7 +2,8 @@
 //   * token embedding plus a hashed row for the (previous token, token) pair, the previous
 //     token of every request kept in a state row on the device;
 //   * root-mean-square norm with one learned number or a weight per coordinate, optionally of
-//     alpha * x + sigmoid(gate) * y (a gated branch joined to the stream before the norm),
+//     alpha * x + sigmoid(gate) * y (a gated branch joined to the stream before the norm), or
+//     of the branch alone with the stream added after it (alpha * x + norm(y)),
 //     optionally with a copy of the result in the activation type for the next product;
 //   * the gated pair of a feed-forward: f(g) * (u + shift) with optional clamps and an
 //     optional per-(token, group) scale (a router's weights);
@@ -14,7 +15,7 @@ namespace {
 __device__ __forceinline__ float sigmoidf_(float z) { return 1.0f / (1.0f + expf(-z)); }
 
 // ------------------------------------------------------------- embedding with pair rows
-// x[t] = table[token] + pairs[row], row = (prev * mul_prev + token * mul_cur) mod buckets,
+// x[t] = table[token] * scale + pairs[row], row = (prev * mul_prev + token * mul_cur) mod buckets,
 // or row `buckets` for a sequence's first token.  prev is the token before in the step, or,
 // for a request's first token of the step, what prev_state[slot] holds; the CTA of that first
 // token then stores the request's last token of the step there.
@@ -25,7 +26,7 @@ __global__ void embed_pair_kernel(float* __restrict__ out, const int* __restrict
                                   int* __restrict__ prev_state, const W* __restrict__ table,
                                   const W* __restrict__ pairs, int n_tokens, int width, int vocab,
                                   long long buckets, long long mul_prev, long long mul_cur,
-                                  int n_slots, int b_cap, int* status) {
+                                  int n_slots, int b_cap, float scale, int* status) {
     prb_grid_launch_dependents();          // (a product that follows may set itself up meanwhile)
     const int t = blockIdx.x;
     if (t >= n_tokens) return;
@@ -52,7 +53,7 @@ __global__ void embed_pair_kernel(float* __restrict__ out, const int* __restrict
     const W* e = table + (size_t)tok * width;
     const W* p = pairs + (size_t)row * width;
     for (int i = threadIdx.x; i < width; i += blockDim.x)
-        o[i] = prb_to_float<W>(e[i]) + prb_to_float<W>(p[i]);
+        o[i] = fmaf(prb_to_float<W>(e[i]), scale, prb_to_float<W>(p[i]));
 }
 
 // ------------------------------------------------------------------------- RMS norm
@@ -69,6 +70,7 @@ struct RmsArgs {
     const int* rows;        // gather, or null
     int n_rows, n_rows_in, width;
     float alpha, eps;
+    int branch_only;        // 1: r = alpha * x + norm(y): the norm is the branch's alone
     int* status;
 };
 
@@ -93,7 +95,7 @@ __global__ void rms_norm_kernel(RmsArgs a) {
     const float* xr = a.x + (size_t)src * width;
     float s = 0.0f;
     for (int i = threadIdx.x; i < width; i += blockDim.x) {
-        float v = a.alpha * xr[i];
+        float v = a.branch_only ? 0.0f : a.alpha * xr[i];
         if (a.y) {
             float yy = a.y[(size_t)src * width + i];
             if (a.gate)
@@ -106,7 +108,8 @@ __global__ void rms_norm_kernel(RmsArgs a) {
     const float ms = prb_block_sum(s, scratch) / (float)width;
     const float inv = (a.gain ? a.gain[0] : 1.0f) / sqrtf(ms + a.eps);
     for (int i = threadIdx.x; i < width; i += blockDim.x) {
-        const float o = row[i] * inv * (a.weight ? a.weight[i] : 1.0f);
+        float o = row[i] * inv * (a.weight ? a.weight[i] : 1.0f);
+        if (a.branch_only) o += a.alpha * xr[i];
         if (a.x_out) a.x_out[(size_t)r * width + i] = o;
         if (out) out[(size_t)r * width + i] = prb_from_float<O>(o);
     }
@@ -227,7 +230,7 @@ PRB_API int prb_embed_pair(float* out, const int* tokens, const int* positions, 
                            const int* q_start, const int* state_slot, int* prev_state,
                            const void* table, const void* pairs, int n_tokens, int width, int vocab,
                            long buckets, long mul_prev, long mul_cur, int n_slots, int b_cap,
-                           int table_dtype, int* status, cudaStream_t stream) {
+                           int table_dtype, float scale, int* status, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (width <= 0 || vocab <= 0 || buckets <= 0 || mul_prev < 0 || mul_cur < 0 ||
         buckets > (1L << 31) || mul_prev >= (1L << 31) || mul_cur >= (1L << 31))
@@ -237,12 +240,12 @@ PRB_API int prb_embed_pair(float* out, const int* tokens, const int* positions, 
         embed_pair_kernel<float><<<n_tokens, threads, 0, stream>>>(
             out, tokens, positions, seq, q_start, state_slot, prev_state, (const float*)table,
             (const float*)pairs, n_tokens, width, vocab, buckets, mul_prev, mul_cur, n_slots, b_cap,
-            status);
+            scale, status);
     else if (table_dtype == PRB_BF16)
         embed_pair_kernel<__nv_bfloat16><<<n_tokens, threads, 0, stream>>>(
             out, tokens, positions, seq, q_start, state_slot, prev_state,
             (const __nv_bfloat16*)table, (const __nv_bfloat16*)pairs, n_tokens, width, vocab,
-            buckets, mul_prev, mul_cur, n_slots, b_cap, status);
+            buckets, mul_prev, mul_cur, n_slots, b_cap, scale, status);
     else
         return PRB_E_DTYPE;
     PRB_LAUNCH_CHECK();
@@ -252,13 +255,15 @@ PRB_API int prb_embed_pair(float* out, const int* tokens, const int* positions, 
 PRB_API int prb_rms_norm(void* out, float* x_out, const float* x, const float* y, const float* gate,
                          long gate_ld, const float* gate_bias, const float* gain,
                          const float* weight, const int* rows, int n_rows, int n_rows_in, int width,
-                         float alpha, float eps, int out_dtype, int* status, cudaStream_t stream) {
+                         float alpha, float eps, int branch_only, int out_dtype, int* status,
+                         cudaStream_t stream) {
     if (n_rows <= 0) return 0;
+    if (branch_only && y == nullptr) return PRB_E_ARG;
     if (width <= 0 || (size_t)width * 4 > 200 * 1024) return PRB_E_SIZE;
     if (out == nullptr && x_out == nullptr) return PRB_E_ARG;
     if (rows != nullptr && x_out == x) return PRB_E_ARG;        // a gather cannot work in place
     RmsArgs a{out, x_out, x, y, gate, gate_ld, gate_bias, gain, weight, rows, n_rows, n_rows_in,
-              width, alpha, eps, status};
+              width, alpha, eps, branch_only, status};
     const int threads = width >= 256 ? 256 : ((width + 31) / 32) * 32;
     const size_t smem = (size_t)width * sizeof(float);
     if (out_dtype == PRB_F32) {

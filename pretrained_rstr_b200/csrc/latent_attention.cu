@@ -42,7 +42,7 @@ latent_prepare_kernel(A* __restrict__ cq, long cq_ld, C* __restrict__ cache,
                       const int* __restrict__ slots, const int* __restrict__ positions,
                       const float* __restrict__ freq, int n_tokens, int q_rank, int rank,
                       int rot_dim, int rot_dims, int page_size, int num_pages, float eps,
-                      int* status) {
+                      float rot_scale, int* status) {
     __shared__ float scratch[32];
     prb_grid_launch_dependents();          // (a product that follows may set itself up meanwhile)
     const int t = blockIdx.x;
@@ -78,11 +78,11 @@ latent_prepare_kernel(A* __restrict__ cq, long cq_ld, C* __restrict__ cache,
         if (i < half) {
             float sn, cs;
             sincosf(pos * freq[i], &sn, &cs);
-            v = r[i] * cs - r[i + half] * sn;
+            v = (r[i] * cs - r[i + half] * sn) * rot_scale;
         } else if (i < rot_dims) {
             float sn, cs;
             sincosf(pos * freq[i - half], &sn, &cs);
-            v = r[i] * cs + r[i - half] * sn;
+            v = (r[i] * cs + r[i - half] * sn) * rot_scale;
         }
         row[rank + i] = prb_from_float<C>(v);
     }
@@ -254,14 +254,15 @@ latent_attention_kernel(float* __restrict__ out, const float* __restrict__ qa,
 
 // grid (ceil(T / LA_GROUP), heads, ceil(vdim / LA_OUT)).  lat: float32 [T, heads, rank]; uvt:
 // [heads, rank, vdim] (the value expansion with the latent axis outermost); out: [T,
-// heads*vdim] in O; gate: float32, head h of token t at gate[t*gate_ld + h], or null.  Like
+// heads*vdim] in O; gate: float32, head h of token t at gate[t*gate_ld + h] (gate_per 1), or
+// one number per value coordinate at gate[t*gate_ld + h*vdim + v] (gate_per vdim), or null.  Like
 // the fold: lane = value coordinate, warp = every eighth latent coordinate, summed in warp
 // order.
 template <typename W, typename O>
 __global__ void __launch_bounds__(LU_THREADS)
 latent_unfold_kernel(O* __restrict__ out, long out_ld, const float* __restrict__ lat,
                      const W* __restrict__ uvt, const float* __restrict__ gate, long gate_ld,
-                     int n_tokens, int heads, int rank, int vdim) {
+                     int gate_per, int n_tokens, int heads, int rank, int vdim) {
     extern __shared__ float ls[];                        // [LA_GROUP][rank]
     __shared__ float part[LU_SLICES][LA_GROUP][LA_OUT];
     const int t0 = blockIdx.x * LA_GROUP, h = blockIdx.y;
@@ -294,7 +295,8 @@ latent_unfold_kernel(O* __restrict__ out, long out_ld, const float* __restrict__
         float sum = part[0][j][l];
 #pragma unroll
         for (int sl = 1; sl < LU_SLICES; ++sl) sum += part[sl][j][l];
-        const float g = gate ? la_sigmoid(gate[(size_t)t * gate_ld + h]) : 1.0f;
+        const float g = gate ? la_sigmoid(gate[(size_t)t * gate_ld + (size_t)h * gate_per +
+                                               (gate_per > 1 ? vv : 0)]) : 1.0f;
         out[(size_t)t * out_ld + h * vdim + vv] = prb_from_float<O>(sum * g);
     }
 }
@@ -305,7 +307,7 @@ PRB_API int prb_latent_prepare(void* cq, long cq_ld, void* cache, const float* p
                                const int* slots, const int* positions, const float* freq,
                                int n_tokens, int q_rank, int rank, int rot_dim, int rot_dims,
                                int page_size, int num_pages, float eps, int cache_dtype,
-                               int act_dtype, int* status, cudaStream_t stream) {
+                               int act_dtype, float rot_scale, int* status, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (rank <= 0 || rot_dim < 0 || rot_dims < 0 || rot_dims > rot_dim || rot_dims % 2 != 0 ||
         page_size <= 0 || (cq != nullptr && q_rank <= 0))
@@ -313,7 +315,7 @@ PRB_API int prb_latent_prepare(void* cq, long cq_ld, void* cache, const float* p
 #define PRB_LP(C, A)                                                                              \
     latent_prepare_kernel<C, A><<<dim3(n_tokens, 2), LA_THREADS, 0, stream>>>(                    \
         (A*)cq, cq_ld, (C*)cache, proj, ld, q_col, kv_col, wq, wkv, slots, positions, freq,       \
-        n_tokens, q_rank, rank, rot_dim, rot_dims, page_size, num_pages, eps, status)
+        n_tokens, q_rank, rank, rot_dim, rot_dims, page_size, num_pages, eps, rot_scale, status)
     if (cache_dtype == PRB_F32 && act_dtype == PRB_F32) PRB_LP(float, float);
     else if (cache_dtype == PRB_BF16 && act_dtype == PRB_BF16) PRB_LP(__nv_bfloat16, __nv_bfloat16);
     else if (cache_dtype == PRB_BF16 && act_dtype == PRB_F32) PRB_LP(__nv_bfloat16, float);
@@ -380,8 +382,9 @@ PRB_API int prb_latent_attention(float* out, const float* qa, const void* cache,
 }
 
 PRB_API int prb_latent_unfold(void* out, long out_ld, const float* lat, const void* uvt,
-                              const float* gate, long gate_ld, int n_tokens, int heads, int rank,
-                              int vdim, int w_dtype, int out_dtype, cudaStream_t stream) {
+                              const float* gate, long gate_ld, int gate_per, int n_tokens,
+                              int heads, int rank, int vdim, int w_dtype, int out_dtype,
+                              cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (heads <= 0 || heads > 65535 || rank <= 0 || vdim <= 0) return PRB_E_SIZE;
     const size_t smem = (size_t)LA_GROUP * rank * sizeof(float);
@@ -389,7 +392,7 @@ PRB_API int prb_latent_unfold(void* out, long out_ld, const float* lat, const vo
     dim3 grid((n_tokens + LA_GROUP - 1) / LA_GROUP, heads, (vdim + LA_OUT - 1) / LA_OUT);
 #define PRB_LU(W, O)                                                                      \
     latent_unfold_kernel<W, O><<<grid, LU_THREADS, smem, stream>>>(                       \
-        (O*)out, out_ld, lat, (const W*)uvt, gate, gate_ld, n_tokens, heads, rank, vdim)
+        (O*)out, out_ld, lat, (const W*)uvt, gate, gate_ld, gate_per, n_tokens, heads, rank, vdim)
     if (w_dtype == PRB_F32 && out_dtype == PRB_F32) PRB_LU(float, float);
     else if (w_dtype == PRB_BF16 && out_dtype == PRB_BF16) PRB_LU(__nv_bfloat16, __nv_bfloat16);
     else if (w_dtype == PRB_BF16 && out_dtype == PRB_F32) PRB_LU(__nv_bfloat16, float);

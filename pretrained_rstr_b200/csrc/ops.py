@@ -132,12 +132,12 @@ def _declare(h: ctypes.CDLL) -> None:
     h.prb_sample_max_top_k.argtypes = []
     h.prb_sample_workspace_words.argtypes = []
     h.prb_sample_workspace_words.restype = c_int
-    h.prb_embed_pair.argtypes = [P, P, P, P, P, P, P, P, P, I, I, I, L, L, L, I, I, I, P, P]
-    h.prb_rms_norm.argtypes = [P, P, P, P, P, L, P, P, P, P, I, I, I, F, F, I, P, P]
+    h.prb_embed_pair.argtypes = [P, P, P, P, P, P, P, P, P, I, I, I, L, L, L, I, I, I, F, P, P]
+    h.prb_rms_norm.argtypes = [P, P, P, P, P, L, P, P, P, P, I, I, I, F, F, I, I, P, P]
     h.prb_gated_pair.argtypes = [P, L, I, P, L, I, I, I, I, F, F, F, P, L, I, I, P]
     h.prb_route.argtypes = [P, P, P, P, L, P, P, I, I, I, I, I, P]
     h.prb_latent_prepare.argtypes = [P, L, P, P, L, I, I, P, P, P, P, P, I, I, I, I, I, I, I, F,
-                                     I, I, P, P]
+                                     I, I, F, P, P]
     h.prb_latent_fold.argtypes = [P, P, L, P, P, P, I, I, I, I, I, I, I, I, P]
     h.prb_latent_attention_mma.argtypes = [P, P, P, L, P, P, P, P, P, P, P, P, I, P, P, P, I, I, I,
                                            I, I, I, F, I, I, I, I, I, P, I, P, P]
@@ -145,7 +145,7 @@ def _declare(h: ctypes.CDLL) -> None:
     h.prb_latent_mma_single_kw.argtypes = [I]
     h.prb_latent_mma_rows.argtypes = []
     h.prb_latent_attention.argtypes = [P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, I, I, P, P]
-    h.prb_latent_unfold.argtypes = [P, L, P, P, P, L, I, I, I, I, I, I, P]
+    h.prb_latent_unfold.argtypes = [P, L, P, P, P, L, I, I, I, I, I, I, I, P]
     h.prb_embed_scaled.argtypes = [P, P, P, P, I, I, I, F, I, P, P]
     h.prb_route_scores.argtypes = [P, P, P, P, L, P, I, I, I, I, I, I, F, I, I, P]
     h.prb_routed_act.argtypes = [P, L, P, L, I, I, I, P, L, I, I, I, I, P]
@@ -188,14 +188,24 @@ def _declare(h: ctypes.CDLL) -> None:
                                          I, I, I, I, I, I, I, I, I, P, P, P, I, P, P]
     h.prb_tmix_finish.argtypes = [P, L, P, L, P, L, I, P, P, I, I, I, F, F, I, P]
     h.prb_wattn_prepare.argtypes = [P, P, P, L, I, I, I, P, P, P, P, P, I, I, I, I, I, I, F, F, I,
-                                    I, I, I, P, P]
+                                    I, I, I, I, P, P, P, P, P]
     h.prb_wattn.argtypes = [P, L, P, P, P, P, P, P, L, P, I, I, I, I, I, I, I, I, I, I, F, F, I, I,
-                            P, P]
+                            P, I, P, P]
     h.prb_wattn_tile_rows.argtypes = [I, I, I, I]
     h.prb_wattn_single_supports.argtypes = [I, I, I, I]
     h.prb_wattn_single.argtypes = list(h.prb_wattn.argtypes)
     h.prb_wattn_tile.argtypes = [P, L, P, P, P, P, P, P, L, P, I, I, I, I, I, I, I, I, I, I, I, F,
-                                 F, I, I, P, P]
+                                 F, I, I, P, I, P, P]
+    h.prb_lru_max_taps.argtypes = []
+    h.prb_lru_conv.argtypes = [P, P, L, I, P, P, P, P, P, P, P, P, I, I, I, I, I, P]
+    h.prb_lru_gates.argtypes = [P, P, P, P, P, P, P, I, I, I, I, P]
+    h.prb_lru_scan.argtypes = [P, L, P, P, P, L, I, I, P, P, P, P, P, P, P, I, I, I, I, I, F, I, P]
+    h.prb_mmem_supports.argtypes = [I, I]
+    h.prb_mmem_step.argtypes = [P, L, P, L, I, I, I, I, I, I, P, P, P, P, P, P, P, P, P, I, I, I,
+                                I, I, I, F, F, F, F, I, P]
+    for name in ("prb_lru_max_taps", "prb_lru_conv", "prb_lru_gates", "prb_lru_scan",
+                 "prb_mmem_supports", "prb_mmem_step"):
+        getattr(h, name).restype = c_int
     for name in ("prb_tmix_lanes", "prb_tmix_shift", "prb_tmix_scan", "prb_tmix_finish",
                  "prb_tmix_step_supports", "prb_tmix_segment", "prb_tmix_max_segments",
                  "prb_tmix_scan_segments",
@@ -873,8 +883,8 @@ def sample(out, logits, n_rows, temperature=None, top_k=None, top_p=None, seeds=
 
 # ------------------------------------------- gated branches, norms after the sum, routers
 def embed_pair(out, tokens, positions, seq_of_token, q_start, state_slot, prev_state, table,
-               pairs, buckets: int, mul_prev: int, mul_cur: int, status) -> None:
-    """out[t,:] = table[tokens[t],:] + pairs[row,:] with row = (prev * mul_prev + token *
+               pairs, buckets: int, mul_prev: int, mul_cur: int, status, scale: float = 1.0) -> None:
+    """out[t,:] = table[tokens[t],:] * scale + pairs[row,:] with row = (prev * mul_prev + token *
     mul_cur) mod buckets, or row ``buckets`` for a sequence's first token; out float32
     [T, width].  ``prev_state`` (int32 [slots]) holds every request's last token between
     steps and is brought up to date by this call."""
@@ -896,13 +906,16 @@ def embed_pair(out, tokens, positions, seq_of_token, q_start, state_slot, prev_s
                                 _p(state_slot), _p(prev_state), _p(table), _p(pairs), n, width,
                                 table.shape[0], buckets, int(mul_prev) % buckets,
                                 int(mul_cur) % buckets, prev_state.numel(), state_slot.numel(),
-                                dtype_code(table.dtype), _p(status), _stream()), what)
+                                dtype_code(table.dtype), float(scale), _p(status), _stream()), what)
 
 
 def rms_norm(x, out=None, x_out=None, y=None, gate=None, gate_bias=None, gain=None, weight=None,
-             rows=None, alpha: float = 1.0, eps: float = 0.0, status=None) -> None:
+             rows=None, alpha: float = 1.0, eps: float = 0.0, status=None,
+             branch_only: bool = False) -> None:
     """v = alpha * x (+ y, or + sigmoid(gate + gate_bias) * y); r = v / sqrt(mean(v^2) + eps)
-    * gain (one number on the device) * weight (per coordinate).  r goes to ``out`` (float32 or
+    * gain (one number on the device) * weight (per coordinate).  ``branch_only``: the norm is
+    the branch's alone and the stream joins after it, r = alpha * x + norm(y) (norm with gain
+    and weight as before).  r goes to ``out`` (float32 or
     bfloat16) and/or ``x_out`` (float32; may be ``x`` itself); with ``rows`` row i of the result
     comes from row rows[i] of the inputs.  ``gate`` may be a column slice of a wider tensor."""
     what = "rms_norm"
@@ -935,7 +948,7 @@ def rms_norm(x, out=None, x_out=None, y=None, gate=None, gate_bias=None, gain=No
         raise KernelArgumentError(f"{what}: fewer input rows than output rows")
     _check(lib().prb_rms_norm(_p(out), _p(x_out), _p(x), _p(y), _p(gate), gate_ld, _p(gate_bias),
                               _p(gain), _p(weight), _p(rows), n_rows, x.shape[0], width,
-                              float(alpha), float(eps),
+                              float(alpha), float(eps), 1 if branch_only else 0,
                               dtype_code(out.dtype) if out is not None else F32, _p(status),
                               _stream()), what)
 
@@ -991,12 +1004,14 @@ def route(scale, chosen, chosen_w, x, w, bias, top: int) -> None:
 
 # ----------------------------------------------------- attention over a shared latent
 def latent_prepare(cq, cache, proj, q_col: int, kv_col: int, wq, wkv, slots, positions, freq,
-                   q_rank: int, rank: int, rot_dim: int, rot_dims: int, eps: float, status) -> None:
+                   q_rank: int, rank: int, rot_dim: int, rot_dims: int, eps: float, status,
+                   rot_scale: float = 1.0) -> None:
     """Per token: the query latent proj[t, q_col : q_col + q_rank], unit-RMS-normed with weight
     ``wq``, goes to ``cq`` ([T, >= q_rank], activation type); the key/value latent
     proj[t, kv_col : kv_col + rank], normed with ``wkv``, and the ``rot_dim`` columns after it,
-    rotated by the token's position, go to the token's cache row (``cache``: [pages, 1,
-    page size, rank + rot_dim]).  ``proj`` is float32 and may be a wider row-major tensor."""
+    rotated by the token's position (and multiplied by ``rot_scale`` where rotated), go to the
+    token's cache row (``cache``: [pages, 1, page size, rank + rot_dim]).  ``proj`` is float32
+    and may be a wider row-major tensor.  ``cq`` None: there is no query latent."""
     what = "latent_prepare"
     if proj.dtype != torch.float32 or proj.stride(1) != 1:
         raise KernelArgumentError(f"{what}: proj must be float32 with unit inner stride")
@@ -1004,22 +1019,27 @@ def latent_prepare(cq, cache, proj, q_col: int, kv_col: int, wq, wkv, slots, pos
     num_pages, kv_heads, page_size, row = cache.shape
     if kv_heads != 1 or row != rank + rot_dim:
         raise KernelArgumentError(f"{what}: the cache must be [pages, 1, page size, {rank + rot_dim}]")
-    if cq.stride(1) != 1 or cq.shape[1] < q_rank or cq.shape[0] < proj.shape[0]:
+    if cq is not None and (cq.stride(1) != 1 or cq.shape[1] < q_rank or cq.shape[0] < proj.shape[0]):
         raise KernelArgumentError(f"{what}: cq has the wrong shape")
     for name, t in (("wq", wq), ("wkv", wkv), ("freq", freq)):
-        _need(t, torch.float32, name, what)
-    if wq.numel() != q_rank or wkv.numel() != rank or freq.numel() < rot_dims // 2 or \
+        if t is not None or name != "wq" or cq is not None:
+            _need(t, torch.float32, name, what)
+    if cq is None:
+        q_rank = 0
+    if (cq is not None and wq.numel() != q_rank) or wkv.numel() != rank or \
+            freq.numel() < rot_dims // 2 or \
             max(q_col + q_rank, kv_col + rank + rot_dim) > proj.shape[1]:
         raise KernelArgumentError(f"{what}: weights or columns do not fit")
     if slots is not None:
         _need(slots, torch.int32, "slots", what)
     _need(positions, torch.int32, "positions", what)
-    _check(lib().prb_latent_prepare(_p(cq), cq.stride(0), _p(cache), _p(proj), proj.stride(0),
+    _check(lib().prb_latent_prepare(_p(cq), 0 if cq is None else cq.stride(0), _p(cache), _p(proj), proj.stride(0),
                                     int(q_col), int(kv_col), _p(wq), _p(wkv), _p(slots),
                                     _p(positions), _p(freq), proj.shape[0], q_rank, rank, rot_dim,
                                     rot_dims, page_size, num_pages, float(eps),
-                                    dtype_code(cache.dtype), dtype_code(cq.dtype), _p(status),
-                                    _stream()), what)
+                                    dtype_code(cache.dtype),
+                                    dtype_code(cache.dtype if cq is None else cq.dtype),
+                                    float(rot_scale), _p(status), _stream()), what)
 
 
 def latent_fold(qa, q, uk, positions, freq, heads: int, dim: int, rot_dim: int, rot_dims: int,
@@ -1066,20 +1086,23 @@ def latent_attention(out, qa, cache, block_table, seq_of_token, positions, sinks
 
 def latent_unfold(out, lat, uvt, gate, heads: int, rank: int, vdim: int) -> None:
     """out[t, h*vdim + v] = sigmoid(gate[t, h]) * sum_r uvt[h, r, v] * lat[t, h, r]; ``gate``
-    float32 [T, heads] (may be a column slice) or None."""
+    float32 [T, heads] (may be a column slice), or [T, heads * vdim]: a gate per value
+    coordinate, or None."""
     what = "latent_unfold"
     _need(lat, torch.float32, "lat", what)
     _need(uvt, None, "uvt", what)
     if tuple(uvt.shape) != (heads, rank, vdim) or tuple(lat.shape[1:]) != (heads, rank) or \
             out.stride(1) != 1 or out.shape[1] < heads * vdim or out.shape[0] < lat.shape[0]:
         raise KernelArgumentError(f"{what}: shapes do not fit")
-    gate_ld = 0
+    gate_ld, gate_per = 0, 1
     if gate is not None:
-        if gate.dtype != torch.float32 or gate.stride(1) != 1 or gate.shape[1] != heads:
-            raise KernelArgumentError(f"{what}: gate must be float32 [T, heads]")
+        if gate.dtype != torch.float32 or gate.stride(1) != 1 or \
+                gate.shape[1] not in (heads, heads * vdim) or gate.shape[0] < lat.shape[0]:
+            raise KernelArgumentError(f"{what}: gate must be float32 [T, heads] or [T, heads * vdim]")
         gate_ld = gate.stride(0)
+        gate_per = vdim if gate.shape[1] == heads * vdim and vdim > 1 else 1
     _check(lib().prb_latent_unfold(_p(out), out.stride(0), _p(lat), _p(uvt), _p(gate), gate_ld,
-                                   lat.shape[0], heads, rank, vdim, dtype_code(uvt.dtype),
+                                   gate_per, lat.shape[0], heads, rank, vdim, dtype_code(uvt.dtype),
                                    dtype_code(out.dtype), _stream()), what)
 
 
@@ -1599,9 +1622,13 @@ def tmix_finish(out, raw, proj, g_col: int, norm_w, seq_of_token, heads: int, vd
 # ------------------------------------------------------------------ windowed attention
 def wattn_prepare(q_out, cache, proj, q_col: int, k_col: int, v_col: int, q_norm, k_norm, slots,
                   positions, freq, heads: int, kv_heads: int, dim: int, vdim: int, rot_dims: int,
-                  eps: float, temp_coef: float, temp_every: int, status=None) -> None:
+                  eps: float, temp_coef: float, temp_every: int, status=None, head_norm=None,
+                  biases=None) -> None:
     """Queries and keys of the step's tokens as the attention reads them: a root-mean-square
-    norm over the whole projection (``q_norm`` / ``k_norm``: float32 weights, or None), the
+    norm over the whole projection (``q_norm`` / ``k_norm``: float32 weights, or None), or per
+    head (``head_norm`` "before": before the rotation, ``q_norm`` / ``k_norm`` of ``dim`` numbers
+    shared by the heads; "after": after the rotation, without weights), ``biases`` = (q, k, v)
+    float32 vectors (or None each) that join the projection first, the
     query's temperature 1 + temp_coef * ln(floor((p + 1) / temp_every) + 1) (``temp_every`` 0:
     none), the rotation of each head's first ``rot_dims`` coordinates (rotate-half).  Queries go
     to q_out float32 [T, heads * dim]; keys and values to the tokens' cache rows [k | v]
@@ -1623,17 +1650,30 @@ def wattn_prepare(q_out, cache, proj, q_col: int, k_col: int, v_col: int, q_norm
         _need(slots, torch.int32, "slots", what)
         if k_col + kv_heads * dim > proj.shape[1] or v_col + kv_heads * vdim > proj.shape[1]:
             raise KernelArgumentError(f"{what}: key or value columns outside the projection")
-    for name, t, size in (("q_norm", q_norm, heads * dim), ("k_norm", k_norm, kv_heads * dim)):
+    if head_norm not in (None, "before", "after"):
+        raise KernelArgumentError(f"{what}: head_norm is None, 'before' or 'after'")
+    mode = {None: 1 if q_norm is not None else 0, "before": 2, "after": 3}[head_norm]
+    for name, t, size in (("q_norm", q_norm, dim if mode == 2 else heads * dim),
+                          ("k_norm", k_norm, dim if mode == 2 else kv_heads * dim)):
         if t is not None:
             _need(t, torch.float32, name, what)
             if t.numel() != size:
                 raise KernelArgumentError(f"{what}: {name} must hold {size} numbers")
+    if mode == 2 and (q_norm is None or (slots is not None and k_norm is None)):
+        raise KernelArgumentError(f"{what}: a norm per head before the rotation has weights")
+    bq, bk, bv = biases if biases is not None else (None, None, None)
+    for name, t, size in (("q bias", bq, heads * dim), ("k bias", bk, kv_heads * dim),
+                          ("v bias", bv, kv_heads * vdim)):
+        if t is not None:
+            _need(t, torch.float32, name, what)
+            if t.numel() != size:
+                raise KernelArgumentError(f"{what}: the {name} must hold {size} numbers")
     _check(lib().prb_wattn_prepare(_p(q_out), _p(cache), _p(proj), proj.stride(0), int(q_col),
                                    int(k_col), int(v_col), _p(q_norm), _p(k_norm), _p(slots),
                                    _p(positions), _p(freq), n, heads, kv_heads, dim, vdim,
                                    int(rot_dims), float(eps), float(temp_coef), int(temp_every),
-                                   page_size, pages, dtype_code(cache.dtype), _p(status),
-                                   _stream()), what)
+                                   page_size, pages, dtype_code(cache.dtype), mode, _p(bq),
+                                   _p(bk), _p(bv), _p(status), _stream()), what)
 
 
 def wattn_tile_rows(heads: int, kv_heads: int, dim: int, vdim: int) -> int:
@@ -1649,11 +1689,14 @@ def wattn_single_supports(heads: int, kv_heads: int, dim: int, vdim: int) -> boo
 
 def wattn(out, q, cache, block_table, seq_of_token, positions, heads: int, dim: int, vdim: int,
           window: int, keep_first: int, scale: float, gate=None, slopes=None,
-          out_scale: float = 1.0, status=None, tile_rows: int = 0, single: bool = False) -> None:
+          out_scale: float = 1.0, status=None, tile_rows: int = 0, single: bool = False,
+          sinks=None, gate_per_value: bool = False) -> None:
     """Softmax attention over cache rows [k | v]: a query at position i sees key j <= i with
     i - j < window (``window`` 0: all) or j < keep_first; score (q . k) * scale - slopes[h] * (i
-    - j); head h's result times sigmoid(gate[t, h]) (``gate``: float32, may be a column slice)
-    times ``out_scale``.  32-bit arithmetic; out in the cache's type.  ``tile_rows`` > 0: the
+    - j); ``sinks`` (float32 [heads]): exp(sinks[h]) joins the softmax's denominator once,
+    without a key or a value; head h's result times sigmoid(gate[t, h]) (``gate``: float32, may
+    be a column slice; ``gate_per_value``: [rows, heads * vdim], a gate per value coordinate) times
+    ``out_scale``.  32-bit arithmetic; out in the cache's type.  ``tile_rows`` > 0: the
     tiled kernel (a CTA per that many consecutive token rows and key/value head).  ``single``:
     the kernel for steps of single tokens (a CTA per (token, key/value head) whose warps share
     out the key blocks; sizes that :func:`wattn_single_supports` takes)."""
@@ -1674,6 +1717,15 @@ def wattn(out, q, cache, block_table, seq_of_token, positions, heads: int, dim: 
                 gate.shape[1] < heads:
             raise KernelArgumentError(f"{what}: gate must be float32 [rows, heads]")
         gate_ld = gate.stride(0)
+    gate_per = 1
+    if gate_per_value:
+        if gate is None or gate.shape[1] < heads * vdim:
+            raise KernelArgumentError(f"{what}: a gate per value coordinate is [rows, heads * vdim]")
+        gate_per = vdim
+    if sinks is not None:
+        _need(sinks, torch.float32, "sinks", what)
+        if sinks.numel() != heads:
+            raise KernelArgumentError(f"{what}: one sink per head")
     if slopes is not None:
         _need(slopes, torch.float32, "slopes", what)
         if slopes.numel() != heads:
@@ -1682,10 +1734,137 @@ def wattn(out, q, cache, block_table, seq_of_token, positions, heads: int, dim: 
               _p(positions), _p(gate), gate_ld, _p(slopes), n, heads, kv_heads, dim, vdim,
               page_size, block_table.shape[1], pages, int(window or 0), int(keep_first or 0))
     tail = (float(scale), float(out_scale), dtype_code(cache.dtype), dtype_code(out.dtype),
-            _p(status), _stream())
+            _p(sinks), gate_per, _p(status), _stream())
     if single:
         _check(lib().prb_wattn_single(*common, *tail), what)
     elif tile_rows > 0:
         _check(lib().prb_wattn_tile(*common, int(tile_rows), *tail), what)
     else:
         _check(lib().prb_wattn(*common, *tail), what)
+
+
+# ------------------------------------------------ recurrent units over a state per request
+def lru_max_taps() -> int:
+    """Most taps of the gated linear recurrence's convolution."""
+    return int(lib().prb_lru_max_taps())
+
+
+def lru_conv(u, proj, x_col: int, x_bias, conv_w, conv_b, conv_state, seq_of_token, positions,
+             q_start, state_slot) -> None:
+    """u[t, c] = conv_b[c] + sum_j conv_w[c, j] * x[t - (taps - 1 - j), c] with x = proj[:, x_col
+    + c] + x_bias[c] (zeros before a sequence's start); the rows before a request's first
+    token of the step come from ``conv_state`` [slots, taps - 1, width] (float32, the latest
+    last).  u float32 [T, width]; ``proj`` float32, may be a wider row-major tensor."""
+    what = "lru_conv"
+    _need(u, torch.float32, "u", what)
+    n, width = u.shape
+    taps = conv_w.shape[1]
+    if proj.dtype != torch.float32 or proj.stride(1) != 1 or proj.shape[0] < n or \
+            x_col + width > proj.shape[1]:
+        raise KernelArgumentError(f"{what}: proj must be float32 [T, >= x_col + width]")
+    for name, t, size in (("x_bias", x_bias, width), ("conv_w", conv_w, width * taps),
+                          ("conv_b", conv_b, width)):
+        if t is not None:
+            _need(t, torch.float32, name, what)
+            if t.numel() != size:
+                raise KernelArgumentError(f"{what}: {name} must hold {size} numbers")
+    _need(conv_state, torch.float32, "conv_state", what)
+    if tuple(conv_state.shape[1:]) != (max(taps - 1, 0), width):
+        raise KernelArgumentError(f"{what}: conv_state must be [slots, taps - 1, width]")
+    for name, t in (("seq_of_token", seq_of_token), ("positions", positions), ("q_start", q_start),
+                    ("state_slot", state_slot)):
+        _need(t, torch.int32, name, what)
+    _check(lib().prb_lru_conv(_p(u), _p(proj), proj.stride(0), int(x_col), _p(x_bias), _p(conv_w),
+                              _p(conv_b), _p(conv_state), _p(seq_of_token), _p(positions),
+                              _p(q_start), _p(state_slot), n, width, taps, conv_state.shape[0],
+                              state_slot.numel(), _stream()), what)
+
+
+def lru_gates(a_out, u, wa_t, wi_t, ba, bi, decay, blocks: int) -> None:
+    """Per token and block b of the channels: r = sigmoid(A_b u_b + ba), i = sigmoid(B_b u_b +
+    bi) (``wa_t`` / ``wi_t``: [blocks, in, out], the block matrices transposed), a = exp(decay
+    * r) to ``a_out`` and sqrt(1 - a^2) * i * u in place of u; 32-bit arithmetic."""
+    what = "lru_gates"
+    _need(a_out, torch.float32, "a_out", what)
+    _need(u, torch.float32, "u", what)
+    n, width = u.shape
+    bw = width // max(1, blocks)
+    _need(wa_t, None, "wa_t", what)
+    _need(wi_t, wa_t.dtype, "wi_t", what)
+    if a_out.shape != u.shape or width % blocks or tuple(wa_t.shape) != (blocks, bw, bw) or \
+            tuple(wi_t.shape) != (blocks, bw, bw):
+        raise KernelArgumentError(f"{what}: shapes do not fit")
+    for name, t in (("ba", ba), ("bi", bi), ("decay", decay)):
+        _need(t, torch.float32, name, what)
+        if t.numel() != width:
+            raise KernelArgumentError(f"{what}: {name} must hold {width} numbers")
+    _check(lib().prb_lru_gates(_p(a_out), _p(u), _p(wa_t), _p(wi_t), _p(ba), _p(bi), _p(decay), n,
+                               width, int(blocks), dtype_code(wa_t.dtype), _stream()), what)
+
+
+def lru_scan(out, a_in, inp, proj, y_col: int, x_col: int, y_bias, x_bias, state, conv_state,
+             q_start, state_slot, positions, n_requests: int, out_scale: float = 1.0) -> None:
+    """S_t = a_t S_(t-1) + inp_t per (request, channel) from and to ``state`` [slots, width]
+    (zero at position 0); out[t, c] = S_t * gelu_tanh(proj[t, y_col + c] + y_bias[c]) *
+    out_scale; ``conv_state`` then holds the request's last taps - 1 inputs proj[:, x_col + c] +
+    x_bias[c]."""
+    what = "lru_scan"
+    _need(a_in, torch.float32, "a_in", what)
+    _need(inp, torch.float32, "inp", what)
+    _need(state, torch.float32, "state", what)
+    _need(conv_state, torch.float32, "conv_state", what)
+    n, width = a_in.shape
+    taps = conv_state.shape[1] + 1
+    if inp.shape != a_in.shape or out.stride(1) != 1 or out.shape[0] < n or out.shape[1] < width or \
+            state.shape[1] != width or conv_state.shape[2] != width or \
+            proj.dtype != torch.float32 or proj.stride(1) != 1 or \
+            max(y_col, x_col) + width > proj.shape[1] or q_start.numel() < n_requests + 1:
+        raise KernelArgumentError(f"{what}: shapes do not fit")
+    _check(lib().prb_lru_scan(_p(out), out.stride(0), _p(a_in), _p(inp), _p(proj), proj.stride(0),
+                              int(y_col), int(x_col), _p(y_bias), _p(x_bias), _p(state),
+                              _p(conv_state), _p(q_start), _p(state_slot), _p(positions), n,
+                              int(n_requests), state.shape[0], width, taps, float(out_scale),
+                              dtype_code(out.dtype), _stream()), what)
+
+
+def mmem_supports(dim: int, vdim: int) -> bool:
+    """Whether the matrix memory's kernel takes heads of these sizes."""
+    return bool(lib().prb_mmem_supports(int(dim), int(vdim)))
+
+
+def mmem_step(out, proj, cols, i_bias, f_bias, norm_w, state_s, state_n, state_m, q_start,
+              state_slot, positions, n_requests: int, heads: int, dim: int, vdim: int, cap: float,
+              q_scale: float, eps: float, out_scale: float = 1.0) -> None:
+    """The matrix memory over the step's tokens, request by request from and to the state
+    slots (``state_s`` [slots, heads, dim, vdim], ``state_n`` [slots, heads, dim], ``state_m``
+    [slots, heads], float32, zero at position 0).  ``cols`` = first columns of (q, k, v, i, f,
+    gate) in ``proj`` (float32 [T, ld]).  out[t, h * vdim + v] = o / rms(o) * norm_w * sigmoid(gate)
+    * out_scale."""
+    what = "mmem_step"
+    if proj.dtype != torch.float32 or proj.stride(1) != 1 or not proj.is_cuda:
+        raise KernelArgumentError(f"{what}: proj must be float32 on CUDA with unit inner stride")
+    n = proj.shape[0]
+    q_col, k_col, v_col, i_col, f_col, g_col = (int(c) for c in cols)
+    if max(q_col + heads * dim, k_col + heads * dim, v_col + heads * vdim, i_col + heads,
+           f_col + heads, g_col + heads * vdim) > proj.shape[1] or out.stride(1) != 1 or \
+            out.shape[0] < n or out.shape[1] < heads * vdim:
+        raise KernelArgumentError(f"{what}: columns outside the tensors")
+    for name, t, shape in (("state_s", state_s, (heads, dim, vdim)), ("state_n", state_n, (heads, dim)),
+                           ("state_m", state_m, (heads,))):
+        _need(t, torch.float32, name, what)
+        if tuple(t.shape[1:]) != shape:
+            raise KernelArgumentError(f"{what}: {name} must be [slots, {', '.join(map(str, shape))}]")
+    for name, t, size in (("i_bias", i_bias, heads), ("f_bias", f_bias, heads),
+                          ("norm_w", norm_w, heads * vdim)):
+        if t is not None:
+            _need(t, torch.float32, name, what)
+            if t.numel() != size:
+                raise KernelArgumentError(f"{what}: {name} must hold {size} numbers")
+    if norm_w is None or q_start.numel() < n_requests + 1:
+        raise KernelArgumentError(f"{what}: norm_w or q_start missing")
+    _check(lib().prb_mmem_step(_p(out), out.stride(0), _p(proj), proj.stride(0), q_col, k_col,
+                               v_col, i_col, f_col, g_col, _p(i_bias), _p(f_bias), _p(norm_w),
+                               _p(state_s), _p(state_n), _p(state_m), _p(q_start), _p(state_slot),
+                               _p(positions), n, int(n_requests), state_s.shape[0], heads, dim,
+                               vdim, float(cap), float(q_scale), float(eps), float(out_scale),
+                               dtype_code(out.dtype), _stream()), what)

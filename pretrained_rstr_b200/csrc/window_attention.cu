@@ -37,6 +37,19 @@ constexpr int NO_WINDOW = 1 << 30;
 
 __device__ __forceinline__ float wa_sigmoid(float z) { return 1.0f / (1.0f + expf(-z)); }
 
+// A learned sink joins a finished softmax: the denominator l (taken against the maximum m)
+// becomes l * f + exp(sink - max(m, sink)) and the weighted sums are multiplied by f.
+__device__ __forceinline__ void wa_join_sink(float sink, float m, float& l, float& f) {
+    const float top = fmaxf(m, sink);
+    f = (m == -INFINITY) ? 0.0f : expf(m - top);
+    l = l * f + expf(sink - top);
+}
+// The gate of head h (gate_per 1: one number a head; else one per value coordinate jj).
+__device__ __forceinline__ float wa_gate(const float* gate, size_t row, int h, int jj, int gate_per) {
+    if (gate == nullptr) return 1.0f;
+    return wa_sigmoid(gate[row + (size_t)h * gate_per + (gate_per > 1 ? jj : 0)]);
+}
+
 // One projection (q or k) of a token: norm over all n numbers, a factor, rotation per head.
 // Element i of head hd goes to dst(hd)[i].
 template <typename D, typename F>
@@ -72,6 +85,69 @@ __device__ __forceinline__ void wa_project(const float* __restrict__ src, int n_
     }
 }
 
+// The same with a norm per HEAD (norm_mode 2: before the rotation, with a weight of `dim`
+// numbers that all heads share; 3: after the rotation, without a weight) and a bias that joins
+// the projection first.  A warp takes a head: its sum of squares is a warp's, whatever the
+// number of heads.
+template <typename D, typename F>
+__device__ __forceinline__ void wa_project_heads(const float* __restrict__ src,
+                                                 const float* __restrict__ bias, int n_heads,
+                                                 int dim, int rot_dims, int norm_mode,
+                                                 const float* __restrict__ norm_w, float eps,
+                                                 float factor, float pos,
+                                                 const float* __restrict__ freq, F dst) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+    const int half = rot_dims / 2;
+    const int units = half + (dim - rot_dims);
+    for (int hd = warp; hd < n_heads; hd += nwarps) {
+        const float* s = src + hd * dim;
+        const float* bb = bias ? bias + hd * dim : nullptr;
+        float inv = 1.0f;
+        if (norm_mode == 2) {
+            float ss = 0.0f;
+            for (int i = lane; i < dim; i += 32) {
+                const float v = s[i] + (bb ? bb[i] : 0.0f);
+                ss = fmaf(v, v, ss);
+            }
+            inv = 1.0f / sqrtf(prb_warp_sum(ss) / (float)dim + eps);
+        } else if (norm_mode == 3) {
+            float ss = 0.0f;
+            for (int u = lane; u < units; u += 32) {
+                if (u < half) {
+                    float sn, cs;
+                    sincosf(pos * freq[u], &sn, &cs);
+                    const float a = s[u] + (bb ? bb[u] : 0.0f);
+                    const float b = s[u + half] + (bb ? bb[u + half] : 0.0f);
+                    const float ra = a * cs - b * sn, rb = b * cs + a * sn;
+                    ss = fmaf(ra, ra, fmaf(rb, rb, ss));
+                } else {
+                    const int i = u - half + rot_dims;
+                    const float v = s[i] + (bb ? bb[i] : 0.0f);
+                    ss = fmaf(v, v, ss);
+                }
+            }
+            inv = 1.0f / sqrtf(prb_warp_sum(ss) / (float)dim + eps);
+        }
+        const float pre = norm_mode == 2 ? inv : 1.0f;
+        const float post = (norm_mode == 3 ? inv : 1.0f) * factor;
+        const float* nw = norm_mode == 2 ? norm_w : nullptr;
+        D* d = dst(hd);
+        for (int u = lane; u < units; u += 32) {
+            if (u < half) {
+                float sn, cs;
+                sincosf(pos * freq[u], &sn, &cs);
+                const float a = (s[u] + (bb ? bb[u] : 0.0f)) * pre * (nw ? nw[u] : 1.0f);
+                const float b = (s[u + half] + (bb ? bb[u + half] : 0.0f)) * pre * (nw ? nw[u + half] : 1.0f);
+                d[u] = prb_from_float<D>((a * cs - b * sn) * post);
+                d[u + half] = prb_from_float<D>((b * cs + a * sn) * post);
+            } else {
+                const int i = u - half + rot_dims;
+                d[i] = prb_from_float<D>((s[i] + (bb ? bb[i] : 0.0f)) * pre * (nw ? nw[i] : 1.0f) * post);
+            }
+        }
+    }
+}
+
 template <typename C>
 __global__ void wattn_prepare_kernel(float* __restrict__ q_out, C* __restrict__ cache,
                                      const float* __restrict__ proj, long ld, int q_col, int k_col,
@@ -81,7 +157,9 @@ __global__ void wattn_prepare_kernel(float* __restrict__ q_out, C* __restrict__ 
                                      const float* __restrict__ freq, int n_tokens, int heads,
                                      int kv_heads, int dim, int vdim, int rot_dims, float eps,
                                      float temp_coef, int temp_every, int page_size, int num_pages,
-                                     int* status) {
+                                     int norm_mode, const float* __restrict__ q_bias,
+                                     const float* __restrict__ k_bias,
+                                     const float* __restrict__ v_bias, int* status) {
     __shared__ float scratch[32];
     prb_grid_launch_dependents();
     const int t = blockIdx.x;
@@ -92,8 +170,13 @@ __global__ void wattn_prepare_kernel(float* __restrict__ q_out, C* __restrict__ 
     float temp = 1.0f;
     if (temp_every > 0) temp = 1.0f + temp_coef * logf((float)((p + 1) / temp_every) + 1.0f);
     float* qo = q_out + (size_t)t * heads * dim;
-    wa_project<float>(row + q_col, heads, dim, rot_dims, q_norm, eps, temp, pos, freq, scratch,
-                      [&](int hd) { return qo + hd * dim; });
+    const bool per_head = norm_mode >= 2 || q_bias != nullptr || k_bias != nullptr;
+    if (per_head)
+        wa_project_heads<float>(row + q_col, q_bias, heads, dim, rot_dims, norm_mode, q_norm, eps,
+                                temp, pos, freq, [&](int hd) { return qo + hd * dim; });
+    else
+        wa_project<float>(row + q_col, heads, dim, rot_dims, q_norm, eps, temp, pos, freq, scratch,
+                          [&](int hd) { return qo + hd * dim; });
     if (slots == nullptr) return;
     const int slot = slots[t];
     if (slot < 0) return;
@@ -105,11 +188,16 @@ __global__ void wattn_prepare_kernel(float* __restrict__ q_out, C* __restrict__ 
     const int rowlen = dim + vdim;
     C* base = cache + (((size_t)page * kv_heads) * page_size + off) * rowlen;
     const size_t head_step = (size_t)page_size * rowlen;
-    wa_project<C>(row + k_col, kv_heads, dim, rot_dims, k_norm, eps, 1.0f, pos, freq, scratch,
-                  [&](int hd) { return base + hd * head_step; });
+    if (per_head)
+        wa_project_heads<C>(row + k_col, k_bias, kv_heads, dim, rot_dims, norm_mode, k_norm, eps,
+                            1.0f, pos, freq, [&](int hd) { return base + hd * head_step; });
+    else
+        wa_project<C>(row + k_col, kv_heads, dim, rot_dims, k_norm, eps, 1.0f, pos, freq, scratch,
+                      [&](int hd) { return base + hd * head_step; });
     for (int u = threadIdx.x; u < kv_heads * vdim; u += blockDim.x) {
         const int g = u / vdim, j = u - g * vdim;
-        base[g * head_step + dim + j] = prb_from_float<C>(row[v_col + u]);
+        base[g * head_step + dim + j] =
+            prb_from_float<C>(row[v_col + u] + (v_bias ? v_bias[u] : 0.0f));
     }
 }
 
@@ -122,7 +210,7 @@ wattn_kernel(O* __restrict__ out, long out_ld, const float* __restrict__ q,
              const float* __restrict__ gate, long gate_ld, const float* __restrict__ slopes,
              int n_tokens, int heads, int kv_heads, int dim, int vdim, int page_size,
              int max_pages, int num_pages, int window, int keep_first, float scale,
-             float out_scale, int* status) {
+             float out_scale, const float* __restrict__ sinks, int gate_per, int* status) {
     extern __shared__ float smem[];
     __shared__ float scratch[32];
     float* qs = smem;                        // [dim]
@@ -212,7 +300,8 @@ wattn_kernel(O* __restrict__ out, long out_ld, const float* __restrict__ q,
         }
         __syncthreads();                         // before the next segment overwrites the weights
     }
-    const float gt = (gate ? wa_sigmoid(gate[(size_t)t * gate_ld + h]) : 1.0f) * out_scale;
+    float fin = 1.0f;                            // the sink joins the denominator, once
+    if (sinks) wa_join_sink(sinks[h], m, l, fin);
 #pragma unroll
     for (int x = 0; x < WA_MAX_V; ++x) {
         part[threadIdx.x] = acc[x];
@@ -221,7 +310,8 @@ wattn_kernel(O* __restrict__ out, long out_ld, const float* __restrict__ q,
         if (kg == 0 && jj < vdim) {
             float tot = 0.0f;
             for (int gg = 0; gg < kgroups; ++gg) tot += part[gg * vthreads + vj];
-            o[jj] = prb_from_float<O>(l > 0.0f ? tot / l * gt : 0.0f);
+            const float gt = wa_gate(gate, (size_t)t * gate_ld, h, jj, gate_per) * out_scale;
+            o[jj] = prb_from_float<O>(l > 0.0f ? tot * fin / l * gt : 0.0f);
         }
         __syncthreads();
     }
@@ -241,7 +331,7 @@ wattn_tile_kernel(O* __restrict__ out, long out_ld, const float* __restrict__ q,
                   const float* __restrict__ gate, long gate_ld, const float* __restrict__ slopes,
                   int n_tokens, int heads, int kv_heads, int dim, int vdim, int page_size,
                   int max_pages, int num_pages, int window, int keep_first, int tq, float scale,
-                  float out_scale, int* status) {
+                  float out_scale, const float* __restrict__ sinks, int gate_per, int* status) {
     extern __shared__ __align__(16) float smem[];
     __shared__ int pages_s[WT_KB];
     prb_grid_launch_dependents();
@@ -427,12 +517,15 @@ wattn_tile_kernel(O* __restrict__ out, long out_ld, const float* __restrict__ q,
             if (pair >= n_pairs) break;
             const int qi = pair / hg, hh = pair - qi * hg;
             const int h = g * hg + hh;
-            const float gt = (gate ? wa_sigmoid(gate[(size_t)(r + qi) * gate_ld + h]) : 1.0f) * out_scale;
+            float fin = 1.0f, lx = l[x];
+            if (sinks) wa_join_sink(sinks[h], m[x], lx, fin);
             O* dst = out + (size_t)(r + qi) * out_ld + (size_t)h * vdim;
 #pragma unroll
             for (int c = 0; c < VC; ++c)
-                if (lane + 32 * c < vdim)
-                    dst[lane + 32 * c] = prb_from_float<O>(l[x] > 0.0f ? acc[x][c] / l[x] * gt : 0.0f);
+                if (lane + 32 * c < vdim) {
+                    const float gt = wa_gate(gate, (size_t)(r + qi) * gate_ld, h, lane + 32 * c, gate_per) * out_scale;
+                    dst[lane + 32 * c] = prb_from_float<O>(lx > 0.0f ? acc[x][c] * fin / lx * gt : 0.0f);
+                }
         }
         r = r1 + 1;
     }
@@ -490,7 +583,7 @@ wattn_single_kernel(O* __restrict__ out, long out_ld, const float* __restrict__ 
                     const float* __restrict__ gate, long gate_ld, const float* __restrict__ slopes,
                     int n_tokens, int heads, int kv_heads, int dim, int vdim, int page_size,
                     int max_pages, int num_pages, int window, int keep_first, float scale,
-                    float out_scale, int* status) {
+                    float out_scale, const float* __restrict__ sinks, int gate_per, int* status) {
     extern __shared__ __align__(16) float smem[];
     __shared__ long long rows_s[WT_WARPS * WT_KB];   // a staged key's row of the cache, or -1
     prb_grid_launch_dependents();
@@ -682,7 +775,12 @@ wattn_single_kernel(O* __restrict__ out, long out_ld, const float* __restrict__ 
                     a = fmaf(splits > 1 ? ws_ld_cluster(st + 2 + jv, ss) : st[2 + jv], f, a);
                 }
             const int h = g * hg + hh;
-            const float gt = (gate ? wa_sigmoid(gate[(size_t)r * gate_ld + h]) : 1.0f) * out_scale;
+            if (sinks) {
+                float fin = 1.0f;
+                wa_join_sink(sinks[h], top, lsum, fin);
+                a *= fin;
+            }
+            const float gt = wa_gate(gate, (size_t)r * gate_ld, h, jv, gate_per) * out_scale;
             orow[e] = prb_from_float<O>(lsum > 0.0f ? a / lsum * gt : 0.0f);
         }
     }
@@ -717,8 +815,11 @@ PRB_API int prb_wattn_prepare(float* q_out, void* cache, const float* proj, long
                               const int* slots, const int* positions, const float* freq,
                               int n_tokens, int heads, int kv_heads, int dim, int vdim, int rot_dims,
                               float eps, float temp_coef, int temp_every, int page_size,
-                              int num_pages, int cache_dtype, int* status, cudaStream_t stream) {
+                              int num_pages, int cache_dtype, int norm_mode, const float* q_bias,
+                              const float* k_bias, const float* v_bias, int* status,
+                              cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
+    if (norm_mode < 0 || norm_mode > 3) return PRB_E_ARG;
     if (heads <= 0 || kv_heads <= 0 || dim <= 0 || vdim <= 0 || rot_dims < 0 || rot_dims % 2 ||
         rot_dims > dim || page_size <= 0)
         return PRB_E_SIZE;
@@ -726,12 +827,12 @@ PRB_API int prb_wattn_prepare(float* q_out, void* cache, const float* proj, long
         wattn_prepare_kernel<float><<<n_tokens, 256, 0, stream>>>(
             q_out, (float*)cache, proj, ld, q_col, k_col, v_col, q_norm, k_norm, slots, positions,
             freq, n_tokens, heads, kv_heads, dim, vdim, rot_dims, eps, temp_coef, temp_every,
-            page_size, num_pages, status);
+            page_size, num_pages, norm_mode, q_bias, k_bias, v_bias, status);
     else if (cache_dtype == PRB_BF16)
         wattn_prepare_kernel<__nv_bfloat16><<<n_tokens, 256, 0, stream>>>(
             q_out, (__nv_bfloat16*)cache, proj, ld, q_col, k_col, v_col, q_norm, k_norm, slots,
             positions, freq, n_tokens, heads, kv_heads, dim, vdim, rot_dims, eps, temp_coef,
-            temp_every, page_size, num_pages, status);
+            temp_every, page_size, num_pages, norm_mode, q_bias, k_bias, v_bias, status);
     else
         return PRB_E_DTYPE;
     PRB_LAUNCH_CHECK();
@@ -743,7 +844,8 @@ PRB_API int prb_wattn(void* out, long out_ld, const float* q, const void* cache,
                       const float* gate, long gate_ld, const float* slopes, int n_tokens, int heads,
                       int kv_heads, int dim, int vdim, int page_size, int max_pages, int num_pages,
                       int window, int keep_first, float scale, float out_scale, int cache_dtype,
-                      int out_dtype, int* status, cudaStream_t stream) {
+                      int out_dtype, const float* sinks, int gate_per, int* status,
+                      cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (heads <= 0 || kv_heads <= 0 || heads % kv_heads != 0 || heads > 65535 || dim <= 0 ||
         vdim <= 0 || vdim > WA_THREADS * WA_MAX_V || page_size <= 0 || max_pages <= 0 ||
@@ -756,7 +858,7 @@ PRB_API int prb_wattn(void* out, long out_ld, const float* q, const void* cache,
     wattn_kernel<CT, OT><<<grid, WA_THREADS, smem, stream>>>(                                    \
         (OT*)out, out_ld, q, (const CT*)cache, block_table, seq_of_token, positions, gate,       \
         gate_ld, slopes, n_tokens, heads, kv_heads, dim, vdim, page_size, max_pages, num_pages,  \
-        window, keep_first, scale, out_scale, status)
+        window, keep_first, scale, out_scale, sinks, gate_per, status)
     if (cache_dtype == PRB_F32 && out_dtype == PRB_F32) WATTN(float, float);
     else if (cache_dtype == PRB_BF16 && out_dtype == PRB_BF16) WATTN(__nv_bfloat16, __nv_bfloat16);
     else return PRB_E_DTYPE;
@@ -779,8 +881,8 @@ PRB_API int prb_wattn_tile(void* out, long out_ld, const float* q, const void* c
                            const float* gate, long gate_ld, const float* slopes, int n_tokens,
                            int heads, int kv_heads, int dim, int vdim, int page_size, int max_pages,
                            int num_pages, int window, int keep_first, int tq, float scale,
-                           float out_scale, int cache_dtype, int out_dtype, int* status,
-                           cudaStream_t stream) {
+                           float out_scale, int cache_dtype, int out_dtype, const float* sinks,
+                           int gate_per, int* status, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     const int most = prb_wattn_tile_rows(heads, kv_heads, dim, vdim);
     if (most <= 0 || kv_heads > 65535 || page_size <= 0 || max_pages <= 0 || window < 0 ||
@@ -797,7 +899,7 @@ PRB_API int prb_wattn_tile(void* out, long out_ld, const float* q, const void* c
         wattn_tile_kernel<CT, OT, VCN><<<grid, WT_WARPS * 32, smem, stream>>>(                   \
             (OT*)out, out_ld, q, (const CT*)cache, block_table, seq_of_token, positions, gate,   \
             gate_ld, slopes, n_tokens, heads, kv_heads, dim, vdim, page_size, max_pages,         \
-            num_pages, window, keep_first, tq, scale, out_scale, status);                        \
+            num_pages, window, keep_first, tq, scale, out_scale, sinks, gate_per, status);       \
     } while (0)
 #define WATT(CT, OT)                                                                             \
     do {                                                                                         \
@@ -827,8 +929,8 @@ PRB_API int prb_wattn_single(void* out, long out_ld, const float* q, const void*
                              const float* gate, long gate_ld, const float* slopes, int n_tokens,
                              int heads, int kv_heads, int dim, int vdim, int page_size,
                              int max_pages, int num_pages, int window, int keep_first, float scale,
-                             float out_scale, int cache_dtype, int out_dtype, int* status,
-                             cudaStream_t stream) {
+                             float out_scale, int cache_dtype, int out_dtype, const float* sinks,
+                             int gate_per, int* status, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (cache_dtype != PRB_F32 && cache_dtype != PRB_BF16) return PRB_E_DTYPE;
     const int csize = cache_dtype == PRB_F32 ? 4 : 2;
@@ -867,7 +969,8 @@ PRB_API int prb_wattn_single(void* out, long out_ld, const float* q, const void*
         cudaLaunchKernelEx(&cfg, wattn_single_kernel<CT, OT, VCN, PN>, (OT*)out, out_ld, q,      \
                            (const CT*)cache, block_table, seq_of_token, positions, gate,         \
                            gate_ld, slopes, n_tokens, heads, kv_heads, dim, vdim, page_size,     \
-                           max_pages, num_pages, window, keep_first, scale, out_scale, status);  \
+                           max_pages, num_pages, window, keep_first, scale, out_scale, sinks,    \
+                           gate_per, status);                                                    \
     } while (0)
 #define WS1(CT, OT, VCN)                                                                         \
     do {                                                                                         \

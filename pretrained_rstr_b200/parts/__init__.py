@@ -1,6 +1,6 @@
 from . import (attention, block, differential_attention, embedding, feed_forward, head,  # noqa: F401  (register)
-               latent_attention, norms, positions, retention, side_by_side, time_mix,
-               window_attention)
+               latent_attention, linear_recurrence, matrix_memory, norms, positions, retention,
+               side_by_side, time_mix, window_attention)
 from .interfaces import (Block, Embedding, FeedForward, Head, KVSpec, LayerCache, Mixer, Norm,
                          PositionEncoding, StateSpec)
 from .linear import Linear

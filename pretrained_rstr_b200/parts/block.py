@@ -163,6 +163,58 @@ class ParallelBlock(Block):
         self.mixer.forward(ctx, h1, x, cache)
 
 
+class BranchNormBlock(Block):
+    """x <- x + norm_1(mixer(x)); x <- x + norm_2(feed_forward(x)): the branches read the stream
+    itself and each branch's RESULT is normed before it joins the stream.  A layer without a
+    feed-forward has the first half only.  Norm and sum are one kernel, which also leaves the
+    stream's copy in the activation type for the next branch's product."""
+    graph_safe = True
+
+    def __init__(self, mixer: Mixer, feed_forward: FeedForward, norms: Dict[str, Norm],
+                 width: int, runtime):
+        self.mixer, self.feed_forward = mixer, feed_forward
+        self.norms = dict(norms)
+        self.width, self.runtime = width, runtime
+        self.has_ff = not getattr(feed_forward, "is_none", False)
+        wanted = {"mixer"} | ({"feed_forward"} if self.has_ff else set())
+        if set(norms) != wanted:
+            raise ValueError(f"branch_norm wants the norms {sorted(wanted)}, got {sorted(norms)}")
+        for part in (mixer, feed_forward):
+            if not getattr(part, "can_overwrite", False):
+                raise ValueError(f"branch_norm: {type(part).__name__} cannot hand over its result "
+                                 f"apart from the stream")
+        for norm in norms.values():
+            if not hasattr(norm, "added"):
+                raise ValueError("branch_norm needs norms that can add a normed branch to the stream")
+
+    def forward(self, ctx, x, cache: LayerCache) -> None:
+        t = x.shape[0]
+        cap = ctx.token_capacity
+        y = ctx.scratch("branch_result", (cap, self.width), torch.float32)[:t]
+        serving = self.runtime.dtype != torch.float32
+        copy = ctx.scratch("stream_copy", (cap, self.width), self.runtime.dtype)[:t] if serving else None
+        # the stream in the products' type: the norm before left it, unless this is the model's
+        # first branch or another kind of block has changed the stream since
+        writer = getattr(ctx, "stream_copy_by", None)
+        current = writer is not None and writer is getattr(ctx, "last_block", None)
+        for name, part in (("mixer", self.mixer), ("feed_forward", self.feed_forward)):
+            if name == "feed_forward" and not self.has_ff:
+                break
+            h = x
+            if serving:
+                if not current:
+                    ops.bias_act(copy, x, None, None, None)
+                h = copy
+            if name == "mixer":
+                part.forward(ctx, h, y, cache, accumulate=False)
+            else:
+                part.forward(ctx, h, y, accumulate=False)
+            self.norms[name].added(ctx, x, y, copy=copy)
+            current = True
+        ctx.stream_copy_by = self
+
+
 register_part("arrangement", "pre_norm", PreNormBlock)
+register_part("arrangement", "branch_norm", BranchNormBlock)
 register_part("arrangement", "post_norm_gated", PostNormGatedBlock)
 register_part("arrangement", "parallel", ParallelBlock)

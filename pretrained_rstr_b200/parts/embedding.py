@@ -43,7 +43,7 @@ class ScaledTokenEmbedding(Embedding):
 
 
 class TokenPairEmbedding(Embedding):
-    """x[t] = table[token] + pairs[row]: a second table indexed by a hash of (previous token,
+    """x[t] = table[token] * scale + pairs[row]: a second table indexed by a hash of (previous token,
     token), row = (prev * mul_prev + token * mul_cur) mod buckets; a sequence's first token
     takes row ``buckets``.  The previous token of every request is state: one int32 per state
     slot on the device, read and brought up to date by the embedding kernel itself, so steps
@@ -51,7 +51,8 @@ class TokenPairEmbedding(Embedding):
     graph_safe = True
 
     def __init__(self, table: torch.Tensor, pairs: torch.Tensor, vocab: int, width: int,
-                 buckets: int, mul_prev: int, mul_cur: int, runtime):
+                 buckets: int, mul_prev: int, mul_cur: int, runtime, scale: float = 1.0):
+        self.scale = float(scale)
         if tuple(table.shape) != (vocab, width) or tuple(pairs.shape) != (buckets + 1, width):
             raise ValueError(f"token_pair_embedding: tables are {list(table.shape)} and "
                              f"{list(pairs.shape)}, expected [{vocab}, {width}] and "
@@ -73,7 +74,7 @@ class TokenPairEmbedding(Embedding):
             raise ValueError("token_pair_embedding adds no position table")
         ops.embed_pair(x, ctx.tokens, ctx.positions, ctx.seq_of_token, ctx.q_start, ctx.state_slot,
                        self.prev, self.table, self.pairs, self.buckets, self.mul_prev,
-                       self.mul_cur, ctx.status)
+                       self.mul_cur, ctx.status, scale=self.scale)
 
 
 register_part("embedding", "token_embedding",
@@ -86,4 +87,5 @@ register_part("embedding", "scaled_token_embedding",
 register_part("embedding", "token_pair_embedding",
               lambda p, store, rt: TokenPairEmbedding(
                   store.get(p["table"], rt.dtype), store.get(p["pairs"], rt.dtype), p["vocab"],
-                  p["width"], p["buckets"], p["mul_prev"], p["mul_cur"], rt))
+                  p["width"], p["buckets"], p["mul_prev"], p["mul_cur"], rt,
+                  scale=p.get("scale", 1.0)))

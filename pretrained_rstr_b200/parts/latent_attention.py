@@ -3,10 +3,17 @@
 Per token the mixer keeps ONE row that all heads share: the normed latent c (``kv_rank``
 numbers) from which a head's keys and values would be expanded, k_h = Uk_h c and
 v_h = Uv_h c, and a rotated key part r (``rot_dim`` numbers) common to the heads.  Queries
-pass a latent of their own: q = Uq norm(Dq h), per head [``dim`` plain | ``rot_dim`` rotated].
+pass a latent of their own, q = Uq norm(Dq h), or (``q_rank`` None) are one matrix, q = Wq h;
+per head [``dim`` plain | ``rot_dim`` rotated].
 The score of head h is (q_plain . k_h + q_rot . r) * scale; a learned sink per head may join
-the softmax's denominator; a head's result may be gated by sigmoid(G h)_h; the output
-projection follows.
+the softmax's denominator; a head's result may be gated by sigmoid(G h)_h (``head_gate``), or
+the concatenated heads element by element by sigmoid(G h) (``value_gate``); the output
+projection follows.  ``window``: position i sees j with 0 <= i - j < window.  The rotation
+pairs coordinate i with i + rot_dims / 2 (``rot_layout`` "half") or 2i with 2i + 1
+("interleaved": the rows of the rotated parts are reordered once, when the model is built,
+which leaves every score as it is); ``rot_scaling`` (factor, original, fast, slow): YaRN's
+frequencies, and its magnitude on cos and sin of both sides, which is one constant on the
+cached rotated key part.
 
 Nothing is expanded per key.  The query is folded through Uk once per token,
 qa_h = [Uk_h^T q_plain | q_rot], so that the score is qa_h . [c | r] and the head's result
@@ -173,7 +180,7 @@ class LatentAttention(Mixer):
         w = p["weights"]
         self.width, self.heads, self.dim = p["width"], p["heads"], p["dim"]
         self.rot_dim, self.vdim = p["rot_dim"], p["vdim"]
-        self.rank, self.q_rank = p["kv_rank"], p["q_rank"]
+        self.rank, self.q_rank = p["kv_rank"], p.get("q_rank")
         self.scale, self.eps = float(p["scale"]), float(p["eps"])
         self.rot_dims, self.window = int(p.get("rot_dims", self.rot_dim)), p.get("window")
         self.runtime = runtime
@@ -186,21 +193,50 @@ class LatentAttention(Mixer):
                 raise ValueError(f"{w[name]}: expected {list(shape)}, found {list(t.shape)}")
             return t
 
+        layout = p.get("rot_layout", "half")
+        if layout not in ("half", "interleaved"):
+            raise ValueError(f"latent_attention: unknown rot_layout {layout!r}")
+        if self.rot_dims % 2 or self.rot_dims > self.rot_dim:
+            raise ValueError(f"latent_attention: {self.rot_dims} rotated coordinates of {self.rot_dim}")
+        # interleaved pairs (2i, 2i + 1) become (i, i + rot_dims / 2): the same reordering of
+        # the rotated query rows and the rotated key rows leaves every dot product as it is
+        order = list(range(self.rot_dim))
+        if layout == "interleaved":
+            order = list(range(0, self.rot_dims, 2)) + list(range(1, self.rot_dims, 2)) + \
+                list(range(self.rot_dims, self.rot_dim))
+        order = torch.tensor(order, dtype=torch.long)
+
+        def reorder_q(m):          # [heads * hd, in]: the last rot_dim rows of every head
+            m = m.reshape(self.heads, hd, m.shape[-1])
+            return torch.cat([m[:, :self.dim], m[:, self.dim:][:, order.to(m.device)]], dim=1) \
+                .reshape(self.heads * hd, -1)
+
+        kv_down = need("kv_down", (self.rank + self.rot_dim, self.width))
+        kv_down = torch.cat([kv_down[:self.rank], kv_down[self.rank:][order.to(kv_down.device)]], dim=0)
         self.input = FusedInput(self.width, runtime, "latent_in")
-        self.input.add("q", need("q_down", (self.q_rank, self.width)))
-        self.input.add("kv", need("kv_down", (self.rank + self.rot_dim, self.width)))
-        self.head_gate = bool(p.get("head_gate", False))
+        self.tensor_cores = dtype == torch.bfloat16 and torch.cuda.is_available() and \
+            ops.latent_mma_supports(self.heads, self.rank, self.rot_dim)
+        if self.q_rank is not None:
+            self.input.add("q", need("q_down", (self.q_rank, self.width)))
+            self.q_norm = need("q_norm", (self.q_rank,)).to(torch.float32).contiguous()
+            q_up = reorder_q(need("q_up", (self.heads * hd, self.q_rank)))
+        else:
+            self.q_norm = None
+            q_up = reorder_q(need("q", (self.heads * hd, self.width)))
+            if not self.tensor_cores:
+                self.input.add("q", q_up)          # the query rides in the first product
+        self.input.add("kv", kv_down)
+        self.value_gate = bool(p.get("value_gate", False))
+        self.head_gate = bool(p.get("head_gate", False)) or self.value_gate
         if self.head_gate:
-            self.input.add("gate", need("gate", (self.heads, self.width)))
-        self.q_norm = need("q_norm", (self.q_rank,)).to(torch.float32).contiguous()
+            rows = self.heads * self.vdim if self.value_gate else self.heads
+            self.input.add("gate", need("gate", (rows, self.width)))
         self.kv_norm = need("kv_norm", (self.rank,)).to(torch.float32).contiguous()
         self.sinks = need("sink", (self.heads,)).to(torch.float32).contiguous() \
             if p.get("sink", False) else None
         # bfloat16 serving: the tensor-core kernel where it takes the sizes, else (and in
         # float32) the 32-bit-arithmetic kernel
-        self.tensor_cores = dtype == torch.bfloat16 and torch.cuda.is_available() and \
-            ops.latent_mma_supports(self.heads, self.rank, self.rot_dim)
-        q_up = need("q_up", (self.heads * hd, self.q_rank))
+        q_in = self.q_rank if self.q_rank is not None else self.width
         k_up = need("k_up", (self.heads * self.dim, self.rank))
         v_up = need("v_up", (self.heads * self.vdim, self.rank))
         out = need("out", (self.width, self.heads * self.vdim))
@@ -208,29 +244,39 @@ class LatentAttention(Mixer):
             # Uk and Uv are folded into their neighbours once, in 32-bit: the query comes out
             # of ONE product as [Uk_h^T q_plain | q_rot] per head, and the output projection
             # takes the heads' gated latent sums as they leave the attention kernel
-            uq = q_up.to(torch.float32).reshape(self.heads, hd, self.q_rank)
+            uq = q_up.to(torch.float32).reshape(self.heads, hd, q_in)
             uk = k_up.to(torch.float32).reshape(self.heads, self.dim, self.rank)
             folded = torch.einsum("hdr,hdq->hrq", uk, uq[:, :self.dim])
             self.q_fold = padded_linear(
                 torch.cat([folded, uq[:, self.dim:]], dim=1).reshape(
-                    self.heads * (self.rank + self.rot_dim), self.q_rank), runtime)
+                    self.heads * (self.rank + self.rot_dim), q_in), runtime)
             uv = v_up.to(torch.float32).reshape(self.heads, self.vdim, self.rank)
             wo = out.to(torch.float32).reshape(self.width, self.heads, self.vdim)
-            self.out_fold = padded_linear(
+            # (a gate per value coordinate acts between Uv and the output projection: they
+            # stay two products then)
+            self.out_fold = None if self.value_gate else padded_linear(
                 torch.einsum("whv,hvr->whr", wo, uv).reshape(self.width, self.heads * self.rank),
                 runtime)
-        else:
-            self.q_up = padded_linear(q_up, runtime)
-            self.uk = k_up.to(dtype).contiguous()
-            # the value expansion with the latent axis outermost: a thread per value
-            # coordinate then reads neighbouring numbers
+        if not self.tensor_cores or self.value_gate:
             self.uvt = v_up.to(dtype).reshape(self.heads, self.vdim, self.rank) \
                 .transpose(1, 2).contiguous()
             self.out = padded_linear(out, runtime)
+        if not self.tensor_cores:
+            self.q_up = padded_linear(q_up, runtime) if self.q_rank is not None else None
+            self.uk = k_up.to(dtype).contiguous()
         half = self.rot_dims // 2
         base = float(p.get("rot_base", 10000.0))
-        self.freq = torch.tensor([base ** (-2.0 * i / self.rot_dims) for i in range(half)] or [0.0],
-                                 dtype=torch.float64).to(torch.float32).to(dev)
+        self.rot_scale = 1.0
+        yarn = p.get("rot_scaling")
+        if yarn:
+            from .positions_rotary import yarn_frequencies
+            self.freq, mag = yarn_frequencies(base, self.rot_dims, float(yarn["factor"]),
+                                              float(yarn["original"]), float(yarn["fast"]),
+                                              float(yarn["slow"]), dev)
+            self.rot_scale = mag * mag         # both sides' magnitudes, on the cached key part
+        else:
+            self.freq = torch.tensor([base ** (-2.0 * i / self.rot_dims) for i in range(half)] or [0.0],
+                                     dtype=torch.float64).to(torch.float32).to(dev)
         self.work_plan = LatentWork()
         self.tile_tokens = self.work_plan.note_mixer(self.heads)
         self.sm_count = ops.sm_count() if torch.cuda.is_available() else 148
@@ -258,25 +304,36 @@ class LatentAttention(Mixer):
         proj = self._proj = self.input.run(ctx, h)
         cols = self.input.cols
         first = self.q_fold if self.tensor_cores else self.q_up
-        cq = ctx.scratch_zero("latent_cq", (cap, first.n_in), dtype)[:t]
-        ops.latent_prepare(cq, cache.k, proj, cols["q"][0], cols["kv"][0], self.q_norm,
-                           self.kv_norm, group.slots if cache.writes else None, ctx.positions,
-                           self.freq, self.q_rank, self.rank, self.rot_dim, self.rot_dims,
-                           self.eps, ctx.status)
+        latent_q = self.q_rank is not None
+        cq = ctx.scratch_zero("latent_cq", (cap, first.n_in), dtype)[:t] if latent_q else None
+        ops.latent_prepare(cq, cache.k, proj, cols["q"][0] if latent_q else 0, cols["kv"][0],
+                           self.q_norm, self.kv_norm, group.slots if cache.writes else None,
+                           ctx.positions, self.freq, self.q_rank or 0, self.rank, self.rot_dim,
+                           self.rot_dims, self.eps, ctx.status, rot_scale=self.rot_scale)
         gate = self.input.view(proj, "gate") if self.head_gate else None
         width = self.rank + self.rot_dim
         if self.tensor_cores:
             # the folded query leaves its product in bfloat16; the attention kernel rotates
             # the rows' last parts as it loads them
             qa = ctx.scratch("latent_qa", (cap, self.heads, width), dtype)[:t]
-            first.forward(ctx, cq, qa.view(t, self.heads * width))
+            first.forward(ctx, cq if latent_q else h, qa.view(t, self.heads * width))
+            if self.value_gate:
+                lat = ctx.scratch("latent_sum", (cap, self.heads, self.rank), torch.float32)[:t]
+                self._attend_tensor_cores(ctx, lat, qa, cache, group, None)
+                o = ctx.scratch_zero("latent_o", (cap, self.out.n_in), dtype)[:t]
+                ops.latent_unfold(o, lat, self.uvt, gate, self.heads, self.rank, self.vdim)
+                self.out.forward(ctx, o, x, resid=x if accumulate else None)
+                return
             gated = ctx.scratch("latent_gated", (cap, self.heads, self.rank), dtype)[:t]
             self._attend_tensor_cores(ctx, gated, qa, cache, group, gate)
             self.out_fold.forward(ctx, gated.view(t, self.heads * self.rank), x,
                                   resid=x if accumulate else None)
             return
-        q = ctx.scratch("latent_q", (cap, first.n_out), torch.float32)[:t]
-        first.forward(ctx, cq, q)
+        if latent_q:
+            q = ctx.scratch("latent_q", (cap, first.n_out), torch.float32)[:t]
+            first.forward(ctx, cq, q)
+        else:
+            q = self.input.view(proj, "q")
         qa = ctx.scratch("latent_qa", (cap, self.heads, width), torch.float32)[:t]
         ops.latent_fold(qa, q, self.uk, ctx.positions, self.freq, self.heads, self.dim,
                         self.rot_dim, self.rot_dims, self.rank)

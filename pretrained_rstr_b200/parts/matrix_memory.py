@@ -1,0 +1,94 @@
+"""A matrix memory with exponential gates and a running maximum (the mLSTM cell of xLSTM), as
+a mixer over a running state instead of cached keys.
+
+Per head, with q = Wq h * ``q_scale``, k = Wk h (``dim`` numbers), v = Wv h (``vdim``) and two
+gate inputs i' = Wi h + bi, f' = Wf h + bf (one number a head each),
+
+    i = cap tanh(i' / cap)                 f = logsigmoid(cap tanh(f' / cap))      (``gate_cap``; 0: none)
+    m_t = max(f + m_(t-1), i)                                                      (m_(-1) = 0)
+    S_t = exp(f + m_(t-1) - m_t) S_(t-1) + exp(i - m_t) k v^T                      (S_(-1) = 0)
+    n_t = exp(f + m_(t-1) - m_t) n_(t-1) + exp(i - m_t) k
+    o_t = S_t^T q / (max(|n_t . q|, exp(-m_t)) + 1e-6)
+
+Each head's o is brought to unit root-mean-square, multiplied by a weight per coordinate and
+by sigmoid(Wg h), and projected.  S, n and m are per-request STATE of the cache manager (a
+slot per live request, zero at position 0), so a prompt may be cut anywhere and decoding is
+the same kernel with one token.  All six projections are one product whose 32-bit result
+feeds the cell unrounded; gates, exponentials, the state and the unit norm are 32-bit.  Sizes,
+the cap, the query's factor, eps and the constant on the result are parameters.
+"""
+from __future__ import annotations
+
+import torch
+
+from ..csrc import ops
+from .interfaces import LayerCache, Mixer, StateSpec
+from .latent_attention import FusedInput
+from .linear import padded_linear
+from .registry import register_part
+
+
+class MatrixMemory(Mixer):
+    graph_safe = True
+    can_overwrite = True
+
+    def __init__(self, p: dict, store, runtime):
+        w = p["weights"]
+        self.width, self.heads = int(p["width"]), int(p["heads"])
+        self.dim, self.vdim = int(p["dim"]), int(p["vdim"])
+        self.cap, self.eps = float(p.get("gate_cap") or 0.0), float(p["eps"])
+        self.q_scale = float(p.get("q_scale", self.dim ** -0.5))
+        self.out_scale = float(p.get("out_scale", 1.0))
+        self.runtime = runtime
+        if torch.cuda.is_available() and not ops.mmem_supports(self.dim, self.vdim):
+            raise ValueError(f"matrix_memory: a head of {self.dim} x {self.vdim} does not fit a "
+                             f"CTA's shared memory")
+
+        def need(name, shape):
+            t = store.get(w[name])
+            if tuple(t.shape) != tuple(shape):
+                raise ValueError(f"{w[name]}: expected {list(shape)}, found {list(t.shape)}")
+            return t
+
+        hk, hv = self.heads * self.dim, self.heads * self.vdim
+        f32 = lambda t: t.to(torch.float32).contiguous()
+        self.input = FusedInput(self.width, runtime, "mmem_in")
+        for name, rows in (("q", hk), ("k", hk), ("v", hv), ("gate", hv), ("i", self.heads),
+                           ("f", self.heads)):
+            self.input.add(name, need(name, (rows, self.width)))
+        self.i_bias = f32(need("i_bias", (self.heads,))) if w.get("i_bias") else None
+        self.f_bias = f32(need("f_bias", (self.heads,))) if w.get("f_bias") else None
+        self.norm = f32(need("norm", (hv,)))
+        self.out = padded_linear(need("out", (self.width, hv)), runtime)
+
+    def state_specs(self):
+        return [StateSpec("mmem_s", (self.heads, self.dim, self.vdim), torch.float32),
+                StateSpec("mmem_n", (self.heads, self.dim), torch.float32),
+                StateSpec("mmem_m", (self.heads,), torch.float32)]
+
+    def step_bytes(self, context: int) -> int:
+        """State bytes a single token reads and writes back, whatever the context."""
+        return 2 * 4 * self.heads * (self.dim * self.vdim + self.dim + 1)
+
+    def fuse_input_rows(self, name: str, weight) -> str:
+        return self.input.add(name, weight)
+
+    def fused_rows(self, name: str):
+        return self.input.view(self._proj, name)
+
+    def forward(self, ctx, h, x, cache: LayerCache, accumulate: bool = True) -> None:
+        t = x.shape[0]
+        cap = ctx.token_capacity
+        proj = self._proj = self.input.run(ctx, h)
+        c = self.input.cols
+        gated = ctx.scratch_zero("mmem_gated", (cap, self.out.n_in), self.runtime.dtype)[:t]
+        ops.mmem_step(gated, proj, (c["q"][0], c["k"][0], c["v"][0], c["i"][0], c["f"][0],
+                                    c["gate"][0]),
+                      self.i_bias, self.f_bias, self.norm, cache.state["mmem_s"],
+                      cache.state["mmem_n"], cache.state["mmem_m"], ctx.q_start, ctx.state_slot,
+                      ctx.positions, ctx.layout.b_cap, self.heads, self.dim, self.vdim, self.cap,
+                      self.q_scale, self.eps, out_scale=self.out_scale)
+        self.out.forward(ctx, gated, x, resid=x if accumulate else None)
+
+
+register_part("mixer", "matrix_memory", lambda p, store, rt: MatrixMemory(p, store, rt))

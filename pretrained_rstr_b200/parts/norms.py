@@ -35,7 +35,8 @@ class RMSNorm(Norm):
     """x / sqrt(mean(x^2) + eps), times one learned number (``gain``) and/or a learned weight
     per coordinate; statistics in 32-bit.  ``joined`` is the same norm of a gated branch
     joined to the stream: x <- norm(alpha x + sigmoid(gate) * y), with an optional copy of the
-    result in the activation type."""
+    result in the activation type.  ``added`` is the norm of a branch alone with the stream
+    joined after it: x <- x + norm(y)."""
     graph_safe = True
     kind = "rms_norm"
 
@@ -63,11 +64,23 @@ class RMSNorm(Norm):
                      weight=self.weight, alpha=alpha, eps=self.eps, status=ctx.status)
 
 
+    def added(self, ctx, x, y, copy=None) -> None:
+        ops.rms_norm(x, out=copy, x_out=x, y=y, gain=self.gain, weight=self.weight, eps=self.eps,
+                     status=ctx.status, branch_only=True)
+
+
 def _rms_norm(params, store, runtime) -> RMSNorm:
     """``scale`` (optional): a constant the result is multiplied by (a head that scales its
-    logits has the constant here, in the 32-bit weight, instead of a pass over the logits)."""
+    logits has the constant here, in the 32-bit weight, instead of a pass over the logits).
+    ``offset`` (optional): the stored weight lies around zero and the norm multiplies by
+    offset + weight (in 32-bit)."""
     gain = store.get(params["gain"]) if params.get("gain") else None
     weight = store.get(params["weight"]) if params.get("weight") else None
+    offset = float(params.get("offset", 0.0))
+    if offset != 0.0:
+        if weight is None:
+            raise ValueError("rms_norm: an offset belongs to a weight per coordinate")
+        weight = weight.to(torch.float32) + offset
     scale = float(params.get("scale", 1.0))
     if scale != 1.0:
         weight = (torch.ones(params["size"], dtype=torch.float32, device=runtime.device)

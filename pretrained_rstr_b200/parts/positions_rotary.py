@@ -6,10 +6,37 @@ from __future__ import annotations
 import torch
 
 
-def rotary_frequencies(base: float, dims: int, device) -> torch.Tensor:
-    """float32 [max(1, dims / 2)] (a table of one zero when nothing is rotated)."""
+def rotary_frequencies(base: float, dims: int, device, divide_by: float = 1.0) -> torch.Tensor:
+    """float32 [max(1, dims / 2)] (a table of one zero when nothing is rotated); ``divide_by``:
+    linear scaling of the positions, every frequency divided by it."""
     if dims < 0 or dims % 2:
         raise ValueError(f"rotary positions need an even number of coordinates, got {dims}")
     half = dims // 2
-    freq = [float(base) ** (-2.0 * i / dims) for i in range(half)] or [0.0]
+    freq = [float(base) ** (-2.0 * i / dims) / float(divide_by) for i in range(half)] or [0.0]
     return torch.tensor(freq, dtype=torch.float64).to(torch.float32).to(device)
+
+
+def yarn_frequencies(base: float, dims: int, factor: float, original: float, fast: float,
+                     slow: float, device):
+    """(frequencies float32 [dims / 2], magnitude) of YaRN-scaled rotary positions.  With
+    d(t) = dims * ln(original / (2 pi t)) / (2 ln base), lo = max(floor(d(fast)), 0), hi =
+    min(ceil(d(slow)), dims - 1) and ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1),
+    frequency i is f_i / factor * ramp_i + f_i * (1 - ramp_i) (fast-turning pairs keep their
+    frequency, slow ones are interpolated), and cos and sin are both multiplied by the
+    magnitude 0.1 * ln(factor) + 1."""
+    import math
+    if dims <= 0 or dims % 2:
+        raise ValueError(f"rotary positions need an even number of coordinates, got {dims}")
+
+    def d_of(t: float) -> float:
+        return dims * math.log(original / (2.0 * math.pi * t)) / (2.0 * math.log(base))
+
+    lo = max(math.floor(d_of(fast)), 0)
+    hi = min(math.ceil(d_of(slow)), dims - 1)
+    freq = []
+    for i in range(dims // 2):
+        f = float(base) ** (-2.0 * i / dims)
+        ramp = min(max((i - lo) / max(hi - lo, 0.001), 0.0), 1.0)
+        freq.append(f / factor * ramp + f * (1.0 - ramp))
+    table = torch.tensor(freq, dtype=torch.float64).to(torch.float32).to(device)
+    return table, 0.1 * math.log(factor) + 1.0

@@ -6,16 +6,24 @@ values ``vdim``.  Every option is a parameter, and a design names the ones it ha
 ``window`` / ``keep_first``  position i sees j <= i with i - j < window, or j < keep_first (the
                       sequence's first tokens stay visible at their true positions); window
                       None or 0: every earlier key
-``rot_dims`` / ``rot_base``  rotary positions on each head's first coordinates (rotate-half)
+``rot_dims`` / ``rot_base``  rotary positions on each head's first coordinates (rotate-half);
+                      ``rot_factor``: every frequency is divided by it (linear scaling)
 ``qk_norm``           a root-mean-square norm over the whole query projection and over the
                       whole key projection before they are split into heads (weights
-                      ``q_norm`` / ``k_norm``)
+                      ``q_norm`` / ``k_norm``); "head": per head, before the rotation, with
+                      weights of ``dim`` numbers that all heads share; "head_after": per head,
+                      after the rotation, without weights
+``bias``              q, k and v have biases (weights ``q_bias`` / ``k_bias`` / ``v_bias``)
+``sink``              a learned number per head (weight ``sink``) whose exponential joins the
+                      softmax's denominator once: it has no key and no value and is not scaled
 ``q_temp``            (coef, every): queries are multiplied by 1 + coef * ln(floor((p + 1) /
                       every) + 1) at position p
 ``slope_bits``        a distance bias slope_h * (i - j) is taken off the scores, slope_h =
                       2^(-slope_bits * (h + 1) / heads); None: no bias
 ``head_gate``         head h's result is multiplied by sigmoid(G x)_h (weight ``gate``, one
                       row a head; it rides in the first product)
+``value_gate``        the concatenated heads are multiplied element by element by sigmoid(G x)
+                      (weight ``gate``, heads * vdim rows; in the first product too)
 ``out_scale``         a constant on the result (a mixer that sums two mixers gives each one)
 ``shares_cache``      the layer has no key/value tensors: it attends over the cache rows
                       another layer wrote, with queries, mask and everything else of its own
@@ -76,14 +84,31 @@ class WindowAttention(Mixer):
         if not self.shares_cache:
             self.input.add("k", need("k", (self.kv_heads * self.dim, self.width)))
             self.input.add("v", need("v", (self.kv_heads * self.vdim, self.width)))
-        self.gated = bool(p.get("head_gate"))
+        self.value_gate = bool(p.get("value_gate"))
+        self.gated = bool(p.get("head_gate")) or self.value_gate
         if self.gated:
-            self.input.add("gate", need("gate", (self.heads, self.width)))
+            rows = self.heads * self.vdim if self.value_gate else self.heads
+            self.input.add("gate", need("gate", (rows, self.width)))
         self.q_norm = self.k_norm = None
-        if p.get("qk_norm"):
+        mode = p.get("qk_norm")
+        if mode not in (None, False, True, "whole", "head", "head_after"):
+            raise ValueError(f"window_attention: unknown qk_norm {mode!r}")
+        self.head_norm = {"head": "before", "head_after": "after"}.get(mode)
+        if mode == "head":
+            self.q_norm = need("q_norm", (self.dim,)).to(torch.float32).contiguous()
+            if not self.shares_cache:
+                self.k_norm = need("k_norm", (self.dim,)).to(torch.float32).contiguous()
+        elif mode in (True, "whole"):
             self.q_norm = need("q_norm", (self.heads * self.dim,)).to(torch.float32).contiguous()
             if not self.shares_cache:
                 self.k_norm = need("k_norm", (self.kv_heads * self.dim,)).to(torch.float32).contiguous()
+        self.biases = None
+        if p.get("bias"):
+            f32 = lambda t: t.to(torch.float32).contiguous()
+            self.biases = (f32(need("q_bias", (self.heads * self.dim,))),
+                           None if self.shares_cache else f32(need("k_bias", (self.kv_heads * self.dim,))),
+                           None if self.shares_cache else f32(need("v_bias", (self.kv_heads * self.vdim,))))
+        self.sinks = need("sink", (self.heads,)).to(torch.float32).contiguous() if p.get("sink") else None
         self.out = padded_linear(need("out", (self.width, self.heads * self.vdim)), runtime)
         self.slopes = None
         if p.get("slope_bits") is not None:
@@ -91,7 +116,8 @@ class WindowAttention(Mixer):
             self.slopes = torch.tensor([2.0 ** (-bits * (h + 1) / self.heads)
                                         for h in range(self.heads)],
                                        dtype=torch.float64).to(torch.float32).to(dev)
-        self.freq = rotary_frequencies(float(p.get("rot_base", 10000.0)), self.rot_dims, dev)
+        self.freq = rotary_frequencies(float(p.get("rot_base", 10000.0)), self.rot_dims, dev,
+                                       divide_by=float(p.get("rot_factor") or 1.0))
         gpu = torch.cuda.is_available()
         self.tile_rows = ops.wattn_tile_rows(self.heads, self.kv_heads, self.dim, self.vdim) if gpu else 0
         self.single_ok = gpu and ops.wattn_single_supports(self.heads, self.kv_heads, self.dim, self.vdim)
@@ -125,7 +151,8 @@ class WindowAttention(Mixer):
                           0 if self.shares_cache else cols["v"][0], self.q_norm, self.k_norm,
                           None if self.shares_cache else group.slots, ctx.positions, self.freq,
                           self.heads, self.kv_heads, self.dim, self.vdim, self.rot_dims, self.eps,
-                          self.temp_coef, self.temp_every, ctx.status)
+                          self.temp_coef, self.temp_every, ctx.status, head_norm=self.head_norm,
+                          biases=self.biases)
         o = ctx.scratch_zero("wattn_out", (cap, self.out.n_in), self.runtime.dtype)[:t]
         # a step of single tokens: a CTA per (token, key/value head) whose warps share out the
         # key blocks (rows of different requests share no keys); sizes that kernel does not
@@ -136,7 +163,8 @@ class WindowAttention(Mixer):
                   gate=proj[:, cols["gate"][0]:] if self.gated else None, slopes=self.slopes,
                   out_scale=self.out_scale, status=ctx.status,
                   tile_rows=min(self.tile_rows, 1) if single else self.tile_rows,
-                  single=single and self.single_ok)
+                  single=single and self.single_ok, sinks=self.sinks,
+                  gate_per_value=self.value_gate)
         self.out.forward(ctx, o, x, resid=x if accumulate else None)
 
 
