@@ -776,7 +776,7 @@ PRB_API int prb_diff_attention_tile(void* out, long out_ld, const float* q, cons
     dim3 grid((n_tokens + tq - 1) / tq, kv_heads);
 #define DIFFT1(CT, OT, VCN)                                                                      \
     do {                                                                                         \
-        if (smem > 48 * 1024)                                                                    \
+        if (smem > 40 * 1024)                                                                    \
             cudaFuncSetAttribute(diff_attention_tile_kernel<CT, OT, VCN>,                        \
                                  cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);        \
         diff_attention_tile_kernel<CT, OT, VCN><<<grid, DT_WARPS * 32, smem, stream>>>(          \
@@ -834,7 +834,7 @@ PRB_API int prb_diff_attention_single(void* out, long out_ld, const float* q, co
     dim3 grid(n_tokens, kv_heads * parts);
 #define DIFFS1(CT, OT, VCN)                                                                      \
     do {                                                                                         \
-        if (smem > 48 * 1024)                                                                    \
+        if (smem > 40 * 1024)                                                                    \
             cudaFuncSetAttribute(diff_attention_single_kernel<CT, OT, VCN>,                      \
                                  cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);        \
         diff_attention_single_kernel<CT, OT, VCN><<<grid, nw * 32, smem, stream>>>(              \

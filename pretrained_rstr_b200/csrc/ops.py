@@ -203,8 +203,14 @@ def _declare(h: ctypes.CDLL) -> None:
     h.prb_mmem_supports.argtypes = [I, I]
     h.prb_mmem_step.argtypes = [P, L, P, L, I, I, I, I, I, I, P, P, P, P, P, P, P, P, P, I, I, I,
                                 I, I, I, F, F, F, F, I, P]
+    h.prb_mmem_segment.argtypes = []
+    h.prb_mmem_max_segments.argtypes = [I, I]
+    h.prb_mmem_scan_supports.argtypes = [I]
+    h.prb_mmem_scan.argtypes = [P, L, P, P, P, L, I, I, I, I, I, I, P, P, P, P, P, P, P, P, P, P,
+                                I, I, I, I, I, I, F, F, F, F, I, P, P, P, P, P, I, I, P]
     for name in ("prb_lru_max_taps", "prb_lru_conv", "prb_lru_gates", "prb_lru_scan",
-                 "prb_mmem_supports", "prb_mmem_step"):
+                 "prb_mmem_supports", "prb_mmem_step", "prb_mmem_segment",
+                 "prb_mmem_max_segments", "prb_mmem_scan_supports", "prb_mmem_scan"):
         getattr(h, name).restype = c_int
     for name in ("prb_tmix_lanes", "prb_tmix_shift", "prb_tmix_scan", "prb_tmix_finish",
                  "prb_tmix_step_supports", "prb_tmix_segment", "prb_tmix_max_segments",
@@ -1836,7 +1842,7 @@ def mmem_step(out, proj, cols, i_bias, f_bias, norm_w, state_s, state_n, state_m
               state_slot, positions, n_requests: int, heads: int, dim: int, vdim: int, cap: float,
               q_scale: float, eps: float, out_scale: float = 1.0) -> None:
     """The matrix memory over the step's tokens, request by request from and to the state
-    slots (``state_s`` [slots, heads, dim, vdim], ``state_n`` [slots, heads, dim], ``state_m``
+    slots (``state_s`` [slots, heads, vdim, dim], ``state_n`` [slots, heads, dim], ``state_m``
     [slots, heads], float32, zero at position 0).  ``cols`` = first columns of (q, k, v, i, f,
     gate) in ``proj`` (float32 [T, ld]).  out[t, h * vdim + v] = o / rms(o) * norm_w * sigmoid(gate)
     * out_scale."""
@@ -1849,7 +1855,7 @@ def mmem_step(out, proj, cols, i_bias, f_bias, norm_w, state_s, state_n, state_m
            f_col + heads, g_col + heads * vdim) > proj.shape[1] or out.stride(1) != 1 or \
             out.shape[0] < n or out.shape[1] < heads * vdim:
         raise KernelArgumentError(f"{what}: columns outside the tensors")
-    for name, t, shape in (("state_s", state_s, (heads, dim, vdim)), ("state_n", state_n, (heads, dim)),
+    for name, t, shape in (("state_s", state_s, (heads, vdim, dim)), ("state_n", state_n, (heads, dim)),
                            ("state_m", state_m, (heads,))):
         _need(t, torch.float32, name, what)
         if tuple(t.shape[1:]) != shape:
@@ -1868,3 +1874,66 @@ def mmem_step(out, proj, cols, i_bias, f_bias, norm_w, state_s, state_n, state_m
                                _p(positions), n, int(n_requests), state_s.shape[0], heads, dim,
                                vdim, float(cap), float(q_scale), float(eps), float(out_scale),
                                dtype_code(out.dtype), _stream()), what)
+
+
+def mmem_segment() -> int:
+    """Tokens of a segment of the matrix memory's scan."""
+    return int(lib().prb_mmem_segment())
+
+
+def mmem_max_segments(t_cap: int, b_cap: int) -> int:
+    """Most segments a step of ``t_cap`` token rows and ``b_cap`` requests can have."""
+    return int(lib().prb_mmem_max_segments(int(t_cap), int(b_cap)))
+
+
+def mmem_scan_supports(dim: int) -> bool:
+    """Whether the scan takes heads of ``dim`` numbers (up to 512)."""
+    return bool(lib().prb_mmem_scan_supports(int(dim)))
+
+
+def mmem_scan(out, raw, gates, proj, cols, i_bias, f_bias, norm_w, state_s, state_n, state_m,
+              q_start, state_slot, positions, seq_of_token, n_requests: int, heads: int, dim: int,
+              vdim: int, cap: float, q_scale: float, eps: float, out_scale: float = 1.0,
+              columns: int = 0, segments=None) -> None:
+    """The same as :func:`mmem_step` for long portions: the tokens' factors first (``gates``
+    float32 [T, heads, 4]), then the linear recurrence with a column of S over neighbouring
+    lanes (``raw`` float32 [T, heads * vdim]; ``columns`` value columns a CTA), then the finish.
+    ``segments`` = (own_s, start_s, own_n, start_n, keep): workspaces of [n, heads, vdim, dim]
+    (two), [n, heads, dim] (two) and [n, heads] for n >= mmem_max_segments segments; with them
+    portions run in segments of 64 tokens side by side."""
+    what = "mmem_scan"
+    if proj.dtype != torch.float32 or proj.stride(1) != 1 or not proj.is_cuda:
+        raise KernelArgumentError(f"{what}: proj must be float32 on CUDA with unit inner stride")
+    n = proj.shape[0]
+    q_col, k_col, v_col, i_col, f_col, g_col = (int(c) for c in cols)
+    _need(raw, torch.float32, "raw", what)
+    _need(gates, torch.float32, "gates", what)
+    if max(q_col + heads * dim, k_col + heads * dim, v_col + heads * vdim, i_col + heads,
+           f_col + heads, g_col + heads * vdim) > proj.shape[1] or out.stride(1) != 1 or \
+            out.shape[0] < n or out.shape[1] < heads * vdim or raw.shape[0] < n or \
+            raw.shape[1] != heads * vdim or gates.numel() < n * heads * 4:
+        raise KernelArgumentError(f"{what}: shapes do not fit")
+    for name, t, shape in (("state_s", state_s, (heads, vdim, dim)), ("state_n", state_n, (heads, dim)),
+                           ("state_m", state_m, (heads,))):
+        _need(t, torch.float32, name, what)
+        if tuple(t.shape[1:]) != shape:
+            raise KernelArgumentError(f"{what}: {name} must be [slots, {', '.join(map(str, shape))}]")
+    _need(norm_w, torch.float32, "norm_w", what)
+    segs, n_seg = (None,) * 5, 0
+    if segments is not None:
+        segs = tuple(segments)
+        n_seg = segs[0].shape[0]
+        for t, shape in zip(segs, ((heads, vdim, dim), (heads, vdim, dim), (heads, dim), (heads, dim), (heads,))):
+            _need(t, torch.float32, "a segment workspace", what)
+            if tuple(t.shape) != (n_seg,) + shape:
+                raise KernelArgumentError(f"{what}: a segment workspace has the wrong shape")
+    code = lib().prb_mmem_scan(_p(out), out.stride(0), _p(raw), _p(gates), _p(proj), proj.stride(0),
+                               q_col, k_col, v_col, i_col, f_col, g_col, _p(i_bias), _p(f_bias),
+                               _p(norm_w), _p(state_s), _p(state_n), _p(state_m), _p(q_start),
+                               _p(state_slot), _p(positions), _p(seq_of_token), n, int(n_requests),
+                               state_s.shape[0], heads, dim, vdim, float(cap), float(q_scale),
+                               float(eps), float(out_scale), int(columns) or vdim,
+                               *(_p(t) for t in segs), n_seg, dtype_code(out.dtype), _stream())
+    _check(code, what)
+    if code == 0 and n > 0:
+        add_launches(4 if segments is not None else 2)

@@ -182,7 +182,7 @@ struct MmemArgs {
     int q_col, k_col, v_col, i_col, f_col, g_col;
     const float* i_bias; const float* f_bias;     // [heads]
     const float* norm_w;                          // [heads * vdim]
-    float* state_s;                               // [slots, heads, dim, vdim]
+    float* state_s;                               // [slots, heads, vdim, dim]
     float* state_n;                               // [slots, heads, dim]
     float* state_m;                               // [slots, heads]
     const int* q_start; const int* state_slot; const int* positions;
@@ -214,7 +214,8 @@ __global__ void __launch_bounds__(MM_THREADS) mmem_step_kernel(MmemArgs a) {
     const int vi = tid % vt, dj = tid / vt;
     const bool live = dj < dsplit;
     const size_t sh = ((size_t)(has_slot ? slot : 0) * a.heads + h);
-    for (int e = tid; e < dim * vdim; e += MM_THREADS) S[e] = carried ? a.state_s[sh * dim * vdim + e] : 0.0f;
+    for (int e = tid; e < dim * vdim; e += MM_THREADS)          // (memory: [vdim][dim])
+        S[(size_t)(e % dim) * vdim + e / dim] = carried ? a.state_s[sh * dim * vdim + e] : 0.0f;
     for (int e = tid; e < dim; e += MM_THREADS) nn[e] = carried ? a.state_n[sh * dim + e] : 0.0f;
     float m = carried ? a.state_m[sh] : 0.0f;
     O* out = reinterpret_cast<O*>(a.out);
@@ -277,9 +278,329 @@ __global__ void __launch_bounds__(MM_THREADS) mmem_step_kernel(MmemArgs a) {
     }
     if (!has_slot) return;
     __syncthreads();
-    for (int e = tid; e < dim * vdim; e += MM_THREADS) a.state_s[sh * dim * vdim + e] = S[e];
+    for (int e = tid; e < dim * vdim; e += MM_THREADS)
+        a.state_s[sh * dim * vdim + e] = S[(size_t)(e % dim) * vdim + e / dim];
     for (int e = tid; e < dim; e += MM_THREADS) a.state_n[sh * dim + e] = nn[e];
     if (tid == 0) a.state_m[sh] = m;
+}
+
+// ------------------------------------------------- (2) the matrix memory, long portions
+// The gates first, for all tokens: the running maximum is a scalar recurrence per (head,
+// request), so a CTA per (head, request) computes the capped gates of 128 tokens side by side,
+// one thread walks the maximum through them, and all threads turn them into the token's
+// factors (keep = exp(f + m_(t-1) - m_t), take = exp(i - m_t), floor = exp(-m_t)).  With the
+// factors known, S and n follow a linear recurrence: a column of S (one value coordinate) is
+// independent of the others and is spread over R neighbouring lanes (NI numbers a lane, in
+// registers; every column's lanes keep a copy of n); the dots with q are closed by shuffles.
+// Portions are cut into segments of 64 tokens that run side by side: pass 1 builds, from
+// zero, what a segment's own tokens add and the product of its keep factors; pass 2 walks a
+// request's segments in order, U_(s+1) = product_s U_s + own_s, from the carried state; pass 3
+// runs every segment from its U_s with outputs, and a request's last segment leaves the state
+// in the slot.  mmem_finish: a warp per (token, head): unit RMS, weight, sigmoid(gate).
+constexpr int MS_BLOCK = 16;        // tokens staged at a time
+constexpr int MS_SEG = 64;          // tokens of a segment
+constexpr int MG_THREADS = 128;
+
+struct MgateArgs {
+    float* gates;                   // [T, heads, 4]: keep, take, floor
+    const float* proj; long ld; int i_col, f_col;
+    const float* i_bias; const float* f_bias;
+    float* state_m;                 // [slots, heads]
+    const int* q_start; const int* state_slot; const int* positions;
+    int n_tokens, n_slots, heads;
+    float cap;
+};
+
+__global__ void __launch_bounds__(MG_THREADS) mmem_gates_kernel(MgateArgs a) {
+    __shared__ float ig_s[MG_THREADS], fg_s[MG_THREADS], m_s[MG_THREADS + 1];
+    prb_grid_launch_dependents();
+    const int h = blockIdx.x, b = blockIdx.y;
+    const int t0 = a.q_start[b], t1 = min(a.q_start[b + 1], a.n_tokens);
+    if (t1 <= t0 || t0 < 0) return;
+    const int slot = a.state_slot[b];
+    const bool has_slot = slot >= 0 && slot < a.n_slots;
+    float m = (has_slot && a.positions[t0] > 0) ? a.state_m[(size_t)slot * a.heads + h] : 0.0f;
+    const float ib = a.i_bias ? a.i_bias[h] : 0.0f, fb = a.f_bias ? a.f_bias[h] : 0.0f;
+    for (int tb = t0; tb < t1; tb += MG_THREADS) {
+        const int nb = min(MG_THREADS, t1 - tb);
+        __syncthreads();
+        if ((int)threadIdx.x < nb) {
+            const float* row = a.proj + (size_t)(tb + threadIdx.x) * a.ld;
+            float ig = row[a.i_col + h] + ib, fg = row[a.f_col + h] + fb;
+            if (a.cap > 0.0f) {
+                ig = a.cap * tanhf(ig / a.cap);
+                fg = a.cap * tanhf(fg / a.cap);
+            }
+            ig_s[threadIdx.x] = ig;
+            fg_s[threadIdx.x] = ru_logsigmoid(fg);
+        }
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            m_s[0] = m;
+            for (int k = 0; k < nb; ++k) m_s[k + 1] = fmaxf(fg_s[k] + m_s[k], ig_s[k]);
+        }
+        __syncthreads();
+        if ((int)threadIdx.x < nb) {
+            const float mp = m_s[threadIdx.x], mn = m_s[threadIdx.x + 1];
+            float* g = a.gates + ((size_t)(tb + threadIdx.x) * a.heads + h) * 4;
+            g[0] = expf(fg_s[threadIdx.x] + mp - mn);
+            g[1] = expf(ig_s[threadIdx.x] - mn);
+            g[2] = expf(-mn);
+        }
+        m = m_s[nb];
+    }
+    if (has_slot && threadIdx.x == 0) a.state_m[(size_t)slot * a.heads + h] = m;
+}
+
+struct MscanArgs {
+    float* o_raw;                   // [T, heads * vdim]
+    const float* proj; long ld; int q_col, k_col, v_col;
+    const float* gates;             // [T, heads, 4]
+    float* state_s;                 // [slots, heads, vdim, dim]
+    float* state_n;                 // [slots, heads, dim]
+    const int* q_start; const int* state_slot; const int* positions;
+    int n_tokens, n_slots, heads, dim, vdim, cols, lanes;
+    float q_scale;
+    int n_requests, seg_len;        // seg_len 0: no segments
+    float* seg_own_s; float* seg_start_s;     // [segments, heads, vdim, dim]
+    float* seg_own_n; float* seg_start_n;     // [segments, heads, dim]
+    float* seg_keep;                          // [segments, heads]
+};
+
+__device__ __forceinline__ bool ms_find_segment(const int* q_start, int n_requests, int seg_len,
+                                                int z, int& b, int& s, int& nseg) {
+    int base = 0;
+    for (b = 0; b < n_requests; ++b) {
+        const int n = q_start[b + 1] - q_start[b];
+        nseg = n > 0 ? (n + seg_len - 1) / seg_len : 0;
+        if (z < base + nseg) {
+            s = z - base;
+            return true;
+        }
+        base += nseg;
+    }
+    return false;
+}
+
+// MODE 0: a whole portion from and to the slot; 1: a segment's own sums from zero; 2: a
+// segment from its start with outputs.
+template <int NI, int MODE>
+__global__ void mmem_scan_kernel(MscanArgs a) {
+    extern __shared__ __align__(16) float smem[];
+    prb_grid_launch_dependents();
+    const int chunk = blockIdx.x, h = blockIdx.y;
+    int b = blockIdx.z, s = 0, nseg = 1;
+    if (MODE != 0 && !ms_find_segment(a.q_start, a.n_requests, a.seg_len, blockIdx.z, b, s, nseg)) return;
+    int t0 = a.q_start[b], t1 = a.q_start[b + 1];
+    if (t1 <= t0 || t0 < 0 || t1 > a.n_tokens) return;
+    const bool carried = a.positions[t0] > 0;
+    if (MODE != 0) {
+        if (MODE == 1 && s == nseg - 1) return;      // (a last segment's own sum is never needed)
+        t0 += s * a.seg_len;
+        t1 = min(t1, t0 + a.seg_len);
+    }
+    const int R = a.lanes, dim_pad = R * NI;
+    float* qs = smem;                               // [MS_BLOCK][dim_pad]
+    float* ks = qs + MS_BLOCK * dim_pad;            // [MS_BLOCK][dim_pad]
+    float* vs = ks + MS_BLOCK * dim_pad;            // [MS_BLOCK][cols]
+    float* gs = vs + MS_BLOCK * a.cols;             // [MS_BLOCK][4]
+    const int r = threadIdx.x % R, c = threadIdx.x / R;
+    const int col = chunk * a.cols + c;
+    const bool live = c < a.cols && col < a.vdim;
+    const int slot = a.state_slot[b];
+    if (slot < 0 || slot >= a.n_slots) return;
+    const size_t column = ((size_t)h * a.vdim + (live ? col : 0)) * a.dim;
+    const size_t per_s = (size_t)a.heads * a.vdim * a.dim, per_n = (size_t)a.heads * a.dim;
+    float* srow = a.state_s + (size_t)slot * per_s + column;
+    float* nrow = a.state_n + (size_t)slot * per_n + (size_t)h * a.dim;
+    float S[NI], N[NI];
+    {
+        const float* from_s = nullptr;
+        const float* from_n = nullptr;
+        if (MODE == 0 && carried) { from_s = srow; from_n = nrow; }
+        if (MODE == 2) {
+            from_s = a.seg_start_s + (size_t)blockIdx.z * per_s + column;
+            from_n = a.seg_start_n + (size_t)blockIdx.z * per_n + (size_t)h * a.dim;
+        }
+#pragma unroll
+        for (int ii = 0; ii < NI; ++ii) {
+            const int i = r * NI + ii;
+            S[ii] = (live && from_s != nullptr && i < a.dim) ? from_s[i] : 0.0f;
+            N[ii] = (from_n != nullptr && i < a.dim) ? from_n[i] : 0.0f;
+        }
+    }
+    float kept = 1.0f;                              // the product of the keep factors (pass 1)
+    for (int tb = t0; tb < t1; tb += MS_BLOCK) {
+        const int nb = min(MS_BLOCK, t1 - tb);
+        __syncthreads();                            // the block before has been consumed
+        for (int u = threadIdx.x; u < nb * a.dim; u += blockDim.x) {
+            const int tok = u / a.dim, i = u - tok * a.dim;
+            const float* row = a.proj + (size_t)(tb + tok) * a.ld + h * a.dim + i;
+            if (MODE != 1) qs[tok * dim_pad + i] = row[a.q_col] * a.q_scale;
+            ks[tok * dim_pad + i] = row[a.k_col];
+        }
+        for (int u = threadIdx.x; u < nb * (dim_pad - a.dim); u += blockDim.x) {
+            const int tok = u / (dim_pad - a.dim), i = a.dim + u % (dim_pad - a.dim);
+            qs[tok * dim_pad + i] = 0.0f;
+            ks[tok * dim_pad + i] = 0.0f;
+        }
+        for (int u = threadIdx.x; u < nb * a.cols; u += blockDim.x) {
+            const int tok = u / a.cols, cc = u - tok * a.cols;
+            const int vc = chunk * a.cols + cc;
+            vs[tok * a.cols + cc] = vc < a.vdim
+                ? a.proj[(size_t)(tb + tok) * a.ld + a.v_col + h * a.vdim + vc] : 0.0f;
+        }
+        for (int u = threadIdx.x; u < nb * 4; u += blockDim.x)
+            gs[u] = a.gates[((size_t)(tb + u / 4) * a.heads + h) * 4 + (u & 3)];
+        __syncthreads();
+#pragma unroll 2
+        for (int tok = 0; tok < nb; ++tok) {
+            const float keep = gs[tok * 4], take = gs[tok * 4 + 1];
+            const float tv = take * (c < a.cols ? vs[tok * a.cols + c] : 0.0f);
+            const float4* q4 = reinterpret_cast<const float4*>(qs + tok * dim_pad + r * NI);
+            const float4* k4 = reinterpret_cast<const float4*>(ks + tok * dim_pad + r * NI);
+            float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f}, nac[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            if (MODE == 1) kept *= keep;
+#pragma unroll
+            for (int g = 0; g < NI / 4; ++g) {      // (sums in an order that dim alone fixes)
+                const float4 kk = k4[g];
+                S[4 * g + 0] = fmaf(keep, S[4 * g + 0], kk.x * tv);
+                S[4 * g + 1] = fmaf(keep, S[4 * g + 1], kk.y * tv);
+                S[4 * g + 2] = fmaf(keep, S[4 * g + 2], kk.z * tv);
+                S[4 * g + 3] = fmaf(keep, S[4 * g + 3], kk.w * tv);
+                N[4 * g + 0] = fmaf(keep, N[4 * g + 0], kk.x * take);
+                N[4 * g + 1] = fmaf(keep, N[4 * g + 1], kk.y * take);
+                N[4 * g + 2] = fmaf(keep, N[4 * g + 2], kk.z * take);
+                N[4 * g + 3] = fmaf(keep, N[4 * g + 3], kk.w * take);
+                if (MODE != 1) {
+                    const float4 qq = q4[g];
+                    acc[0] = fmaf(S[4 * g + 0], qq.x, acc[0]);
+                    acc[1] = fmaf(S[4 * g + 1], qq.y, acc[1]);
+                    acc[2] = fmaf(S[4 * g + 2], qq.z, acc[2]);
+                    acc[3] = fmaf(S[4 * g + 3], qq.w, acc[3]);
+                    nac[0] = fmaf(N[4 * g + 0], qq.x, nac[0]);
+                    nac[1] = fmaf(N[4 * g + 1], qq.y, nac[1]);
+                    nac[2] = fmaf(N[4 * g + 2], qq.z, nac[2]);
+                    nac[3] = fmaf(N[4 * g + 3], qq.w, nac[3]);
+                }
+            }
+            if (MODE != 1) {
+                float o = (acc[0] + acc[1]) + (acc[2] + acc[3]);
+                float nq = (nac[0] + nac[1]) + (nac[2] + nac[3]);
+                for (int m = 1; m < R; m <<= 1) {
+                    o += __shfl_xor_sync(0xffffffffu, o, m);
+                    nq += __shfl_xor_sync(0xffffffffu, nq, m);
+                }
+                if (live && r == 0)
+                    a.o_raw[(size_t)(tb + tok) * a.heads * a.vdim + h * a.vdim + col] =
+                        o / (fmaxf(fabsf(nq), gs[tok * 4 + 2]) + 1e-6f);
+            }
+        }
+    }
+    float* to_s = nullptr;
+    float* to_n = nullptr;
+    if (MODE == 0 || (MODE == 2 && s == nseg - 1)) { to_s = srow; to_n = nrow; }
+    if (MODE == 1) {
+        to_s = a.seg_own_s + (size_t)blockIdx.z * per_s + column;
+        to_n = a.seg_own_n + (size_t)blockIdx.z * per_n + (size_t)h * a.dim;
+        if (chunk == 0 && threadIdx.x == 0) a.seg_keep[(size_t)blockIdx.z * a.heads + h] = kept;
+    }
+    if (to_s != nullptr) {
+#pragma unroll
+        for (int ii = 0; ii < NI; ++ii) {
+            const int i = r * NI + ii;
+            if (i >= a.dim) continue;
+            if (live) to_s[i] = S[ii];
+            if (chunk == 0 && c == 0) to_n[i] = N[ii];
+        }
+    }
+}
+
+// Pass 2: a thread per state number of a (head, request), the request's segments in order.
+__global__ void mmem_carry_kernel(MscanArgs a) {
+    prb_grid_launch_dependents();
+    const int h = blockIdx.x, b = blockIdx.y;
+    const int t0 = a.q_start[b], t1 = a.q_start[b + 1];
+    if (t1 <= t0 || t0 < 0 || t1 > a.n_tokens) return;
+    const int slot = a.state_slot[b];
+    if (slot < 0 || slot >= a.n_slots) return;
+    int base = 0;
+    for (int bb = 0; bb < b; ++bb) {
+        const int n = a.q_start[bb + 1] - a.q_start[bb];
+        base += n > 0 ? (n + a.seg_len - 1) / a.seg_len : 0;
+    }
+    const int nseg = (t1 - t0 + a.seg_len - 1) / a.seg_len;
+    const size_t per_s = (size_t)a.heads * a.vdim * a.dim, per_n = (size_t)a.heads * a.dim;
+    const size_t head_s = (size_t)a.vdim * a.dim;
+    const bool carried = a.positions[t0] > 0;
+    for (size_t e = (size_t)blockIdx.z * 1024 + threadIdx.x;
+         e < min(head_s, ((size_t)blockIdx.z + 1) * 1024); e += blockDim.x) {
+        const size_t at = (size_t)h * head_s + e;
+        float S = carried ? a.state_s[(size_t)slot * per_s + at] : 0.0f;
+        for (int s = 0; s < nseg; ++s) {
+            a.seg_start_s[(size_t)(base + s) * per_s + at] = S;
+            if (s + 1 < nseg)
+                S = fmaf(a.seg_keep[(size_t)(base + s) * a.heads + h], S,
+                         a.seg_own_s[(size_t)(base + s) * per_s + at]);
+        }
+    }
+    if (blockIdx.z == 0) {
+        for (int e = threadIdx.x; e < a.dim; e += blockDim.x) {
+            const size_t at = (size_t)h * a.dim + e;
+            float N = carried ? a.state_n[(size_t)slot * per_n + at] : 0.0f;
+            for (int s = 0; s < nseg; ++s) {
+                a.seg_start_n[(size_t)(base + s) * per_n + at] = N;
+                if (s + 1 < nseg)
+                    N = fmaf(a.seg_keep[(size_t)(base + s) * a.heads + h], N,
+                             a.seg_own_n[(size_t)(base + s) * per_n + at]);
+            }
+        }
+    }
+}
+
+template <typename O>
+__global__ void mmem_finish_kernel(O* __restrict__ out, long out_ld, const float* __restrict__ o_raw,
+                                   const float* __restrict__ proj, long ld, int g_col,
+                                   const float* __restrict__ norm_w, const int* __restrict__ seq,
+                                   int n_tokens, int heads, int vdim, float eps, float out_scale) {
+    prb_grid_launch_dependents();
+    const int lane = threadIdx.x & 31;
+    const size_t pair = (size_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (pair >= (size_t)n_tokens * heads) return;
+    const int t = (int)(pair / heads), h = (int)(pair % heads);
+    O* o = out + (size_t)t * out_ld + (size_t)h * vdim;
+    if (seq[t] < 0) {
+        for (int j = lane; j < vdim; j += 32) o[j] = prb_from_float<O>(0.0f);
+        return;
+    }
+    const float* raw = o_raw + ((size_t)t * heads + h) * vdim;
+    float ss = 0.0f;
+    for (int j = lane; j < vdim; j += 32) ss = fmaf(raw[j], raw[j], ss);
+    const float inv = 1.0f / sqrtf(prb_warp_sum(ss) / (float)vdim + eps);
+    const float* g = proj + (size_t)t * ld + g_col + h * vdim;
+    for (int j = lane; j < vdim; j += 32)
+        o[j] = prb_from_float<O>(raw[j] * inv * norm_w[h * vdim + j] * ru_sigmoid(g[j]) * out_scale);
+}
+
+int ms_ni(int dim) { return dim <= 128 ? 4 : 16; }
+int ms_lanes(int dim) {
+    if (dim <= 0) return 0;
+    const int ni = ms_ni(dim);
+    int r = 1;
+    while (r * ni < dim) r <<= 1;
+    return r <= 32 ? r : 0;
+}
+
+template <int NI>
+void ms_launch(const MscanArgs& a, int mode, dim3 grid, int threads, size_t smem, cudaStream_t stream) {
+    if (smem > 40 * 1024) {
+        cudaFuncSetAttribute(mmem_scan_kernel<NI, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaFuncSetAttribute(mmem_scan_kernel<NI, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaFuncSetAttribute(mmem_scan_kernel<NI, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    }
+    if (mode == 0) mmem_scan_kernel<NI, 0><<<grid, threads, smem, stream>>>(a);
+    else if (mode == 1) mmem_scan_kernel<NI, 1><<<grid, threads, smem, stream>>>(a);
+    else mmem_scan_kernel<NI, 2><<<grid, threads, smem, stream>>>(a);
 }
 
 size_t mmem_smem(int dim, int vdim) {
@@ -317,12 +638,12 @@ PRB_API int prb_lru_gates(float* a_out, float* u, const void* wa_t, const void* 
     if (smem > 160 * 1024) return PRB_E_SIZE;
     dim3 grid((n_tokens + LRU_TOK - 1) / LRU_TOK, blocks);
     if (w_dtype == PRB_F32) {
-        if (smem > 48 * 1024)
+        if (smem > 40 * 1024)
             cudaFuncSetAttribute(lru_gates_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         lru_gates_kernel<float><<<grid, 128, smem, stream>>>(
             a_out, u, (const float*)wa_t, (const float*)wi_t, ba, bi, decay, n_tokens, width, bw);
     } else if (w_dtype == PRB_BF16) {
-        if (smem > 48 * 1024)
+        if (smem > 40 * 1024)
             cudaFuncSetAttribute(lru_gates_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         lru_gates_kernel<__nv_bfloat16><<<grid, 128, smem, stream>>>(
             a_out, u, (const __nv_bfloat16*)wa_t, (const __nv_bfloat16*)wi_t, ba, bi, decay,
@@ -378,16 +699,88 @@ PRB_API int prb_mmem_step(void* out, long out_ld, const float* proj, long ld, in
     const size_t smem = mmem_smem(dim, vdim);
     dim3 grid(heads, n_requests);
     if (out_dtype == PRB_F32) {
-        if (smem > 48 * 1024)
+        if (smem > 40 * 1024)
             cudaFuncSetAttribute(mmem_step_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         mmem_step_kernel<float><<<grid, MM_THREADS, smem, stream>>>(a);
     } else if (out_dtype == PRB_BF16) {
-        if (smem > 48 * 1024)
+        if (smem > 40 * 1024)
             cudaFuncSetAttribute(mmem_step_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         mmem_step_kernel<__nv_bfloat16><<<grid, MM_THREADS, smem, stream>>>(a);
     } else {
         return PRB_E_DTYPE;
     }
+    PRB_LAUNCH_CHECK();
+    return 0;
+}
+
+// Tokens of a segment, the most segments a step of `t_cap` token rows and `b_cap` requests can
+// have (what the workspaces are sized for), and whether the scan takes heads of `dim`.
+PRB_API int prb_mmem_segment() { return MS_SEG; }
+PRB_API int prb_mmem_max_segments(int t_cap, int b_cap) { return t_cap / MS_SEG + b_cap; }
+PRB_API int prb_mmem_scan_supports(int dim) { return ms_lanes(dim) > 0 ? 1 : 0; }
+
+// The matrix memory over long portions: gates, scan (one CTA per (columns, head, request), or,
+// with workspaces, in segments side by side), finish.  `gates`: [T, heads, 4]; `o_raw`: [T,
+// heads * vdim]; workspaces: seg_s two of [segments, heads, vdim, dim], seg_n two of [segments,
+// heads, dim], seg_keep [segments, heads].  The state is [slots, heads, vdim, dim].
+PRB_API int prb_mmem_scan(void* out, long out_ld, float* o_raw, float* gates, const float* proj,
+                          long ld, int q_col, int k_col, int v_col, int i_col, int f_col,
+                          int g_col, const float* i_bias, const float* f_bias,
+                          const float* norm_w, float* state_s, float* state_n, float* state_m,
+                          const int* q_start, const int* state_slot, const int* positions,
+                          const int* seq_of_token, int n_tokens, int n_requests, int n_slots,
+                          int heads, int dim, int vdim, float cap, float q_scale, float eps,
+                          float out_scale, int cols, float* seg_own_s, float* seg_start_s,
+                          float* seg_own_n, float* seg_start_n, float* seg_keep, int segments,
+                          int out_dtype, cudaStream_t stream) {
+    if (n_tokens <= 0 || n_requests <= 0) return 0;
+    const int lanes = ms_lanes(dim);
+    if (heads <= 0 || heads > 65535 || n_requests > 65535 || vdim <= 0 || lanes == 0 || cols <= 0)
+        return PRB_E_SIZE;
+    if (ld % 4 != 0 || ((uintptr_t)proj) % 16 != 0) return PRB_E_ALIGN;
+    if (out_dtype != PRB_F32 && out_dtype != PRB_BF16) return PRB_E_DTYPE;
+    const bool segmented = seg_own_s && seg_start_s && seg_own_n && seg_start_n && seg_keep && segments > 0;
+    if (segmented && (segments > 65535 || segments < prb_mmem_max_segments(n_tokens, n_requests)))
+        return PRB_E_SIZE;
+    MgateArgs g{gates, proj, ld, i_col, f_col, i_bias, f_bias, state_m, q_start, state_slot,
+                positions, n_tokens, n_slots, heads, cap};
+    mmem_gates_kernel<<<dim3(heads, n_requests), MG_THREADS, 0, stream>>>(g);
+    PRB_LAUNCH_CHECK();
+    if (cols > vdim) cols = vdim;
+    while (cols * lanes > 1024) cols = (cols + 1) / 2;
+    const int threads = (cols * lanes + 31) / 32 * 32;
+    const int chunks = (vdim + cols - 1) / cols;
+    const int ni = ms_ni(dim);
+    MscanArgs a{o_raw, proj, ld, q_col, k_col, v_col, gates, state_s, state_n, q_start, state_slot,
+                positions, n_tokens, n_slots, heads, dim, vdim, cols, lanes, q_scale, n_requests,
+                segmented ? MS_SEG : 0, seg_own_s, seg_start_s, seg_own_n, seg_start_n, seg_keep};
+    const size_t smem = (size_t)MS_BLOCK * (2 * lanes * ni + cols + 4) * sizeof(float);
+    if (!segmented) {
+        const dim3 grid(chunks, heads, n_requests);
+        if (ni == 4) ms_launch<4>(a, 0, grid, threads, smem, stream);
+        else ms_launch<16>(a, 0, grid, threads, smem, stream);
+        PRB_LAUNCH_CHECK();
+    } else {
+        const dim3 grid(chunks, heads, prb_mmem_max_segments(n_tokens, n_requests));
+        if (ni == 4) ms_launch<4>(a, 1, grid, threads, smem, stream);
+        else ms_launch<16>(a, 1, grid, threads, smem, stream);
+        PRB_LAUNCH_CHECK();
+        mmem_carry_kernel<<<dim3(heads, n_requests, ((size_t)vdim * dim + 1023) / 1024), 256, 0, stream>>>(a);
+        PRB_LAUNCH_CHECK();
+        if (ni == 4) ms_launch<4>(a, 2, grid, threads, smem, stream);
+        else ms_launch<16>(a, 2, grid, threads, smem, stream);
+        PRB_LAUNCH_CHECK();
+    }
+    const int warps = 4;
+    const unsigned blocks = (unsigned)(((size_t)n_tokens * heads + warps - 1) / warps);
+    if (out_dtype == PRB_F32)
+        mmem_finish_kernel<float><<<blocks, warps * 32, 0, stream>>>(
+            (float*)out, out_ld, o_raw, proj, ld, g_col, norm_w, seq_of_token, n_tokens, heads,
+            vdim, eps, out_scale);
+    else
+        mmem_finish_kernel<__nv_bfloat16><<<blocks, warps * 32, 0, stream>>>(
+            (__nv_bfloat16*)out, out_ld, o_raw, proj, ld, g_col, norm_w, seq_of_token, n_tokens,
+            heads, vdim, eps, out_scale);
     PRB_LAUNCH_CHECK();
     return 0;
 }

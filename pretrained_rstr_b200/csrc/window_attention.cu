@@ -893,7 +893,7 @@ PRB_API int prb_wattn_tile(void* out, long out_ld, const float* q, const void* c
     dim3 grid((n_tokens + tq - 1) / tq, kv_heads);
 #define WATT1(CT, OT, VCN)                                                                       \
     do {                                                                                         \
-        if (smem > 48 * 1024)                                                                    \
+        if (smem > 40 * 1024)       /* (static shared memory counts toward the 48 KB too) */ \
             cudaFuncSetAttribute(wattn_tile_kernel<CT, OT, VCN>,                                 \
                                  cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);        \
         wattn_tile_kernel<CT, OT, VCN><<<grid, WT_WARPS * 32, smem, stream>>>(                   \
@@ -963,7 +963,7 @@ PRB_API int prb_wattn_single(void* out, long out_ld, const float* q, const void*
     cfg.numAttrs = splits > 1 ? 1 : 0;
 #define WS2(CT, OT, VCN, PN)                                                                     \
     do {                                                                                         \
-        if (smem > 48 * 1024)                                                                    \
+        if (smem > 40 * 1024)       /* (static shared memory counts toward the 48 KB too) */ \
             cudaFuncSetAttribute(wattn_single_kernel<CT, OT, VCN, PN>,                           \
                                  cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);        \
         cudaLaunchKernelEx(&cfg, wattn_single_kernel<CT, OT, VCN, PN>, (OT*)out, out_ld, q,      \

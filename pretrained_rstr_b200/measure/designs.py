@@ -49,11 +49,12 @@ def weight_bytes(m) -> int:
     from ..config.registry import lookup
     arch = lookup(m.config.to_dict())
     total = 0
+    head = m.config.head_spec().params.get("weights")      # (a token table that is the head counts)
     for name, exp in arch.expected_tensors(m.config).items():
         n = 1
         for s in exp.shape:
             n *= s
-        if name in ("wpe.weight", "embed", "bigram"):
+        if name in ("wpe.weight", "embed", "bigram") and name != head:
             continue
         total += 2 * n
     return total

@@ -13,7 +13,9 @@ gate inputs i' = Wi h + bi, f' = Wf h + bf (one number a head each),
 Each head's o is brought to unit root-mean-square, multiplied by a weight per coordinate and
 by sigmoid(Wg h), and projected.  S, n and m are per-request STATE of the cache manager (a
 slot per live request, zero at position 0), so a prompt may be cut anywhere and decoding is
-the same kernel with one token.  All six projections are one product whose 32-bit result
+the same kernels with one token.  Steps of few tokens are one launch (a CTA per (head,
+request) with the state in shared memory); longer portions compute the tokens' gate factors
+first and then run the linear recurrence in segments of 64 tokens side by side.  All six projections are one product whose 32-bit result
 feeds the cell unrounded; gates, exponentials, the state and the unit norm are 32-bit.  Sizes,
 the cap, the query's factor, eps and the constant on the result are parameters.
 """
@@ -60,9 +62,11 @@ class MatrixMemory(Mixer):
         self.f_bias = f32(need("f_bias", (self.heads,))) if w.get("f_bias") else None
         self.norm = f32(need("norm", (hv,)))
         self.out = padded_linear(need("out", (self.width, hv)), runtime)
+        self.scan_ok = torch.cuda.is_available() and ops.mmem_scan_supports(self.dim)
+        self.sm_count = ops.sm_count() if torch.cuda.is_available() else 148
 
     def state_specs(self):
-        return [StateSpec("mmem_s", (self.heads, self.dim, self.vdim), torch.float32),
+        return [StateSpec("mmem_s", (self.heads, self.vdim, self.dim), torch.float32),
                 StateSpec("mmem_n", (self.heads, self.dim), torch.float32),
                 StateSpec("mmem_m", (self.heads,), torch.float32)]
 
@@ -82,12 +86,35 @@ class MatrixMemory(Mixer):
         proj = self._proj = self.input.run(ctx, h)
         c = self.input.cols
         gated = ctx.scratch_zero("mmem_gated", (cap, self.out.n_in), self.runtime.dtype)[:t]
-        ops.mmem_step(gated, proj, (c["q"][0], c["k"][0], c["v"][0], c["i"][0], c["f"][0],
-                                    c["gate"][0]),
-                      self.i_bias, self.f_bias, self.norm, cache.state["mmem_s"],
-                      cache.state["mmem_n"], cache.state["mmem_m"], ctx.q_start, ctx.state_slot,
-                      ctx.positions, ctx.layout.b_cap, self.heads, self.dim, self.vdim, self.cap,
-                      self.q_scale, self.eps, out_scale=self.out_scale)
+        columns = (c["q"][0], c["k"][0], c["v"][0], c["i"][0], c["f"][0], c["gate"][0])
+        states = (cache.state["mmem_s"], cache.state["mmem_n"], cache.state["mmem_m"])
+        requests = ctx.layout.b_cap
+        if ctx.layout.t_cap <= ops.mmem_segment() or not self.scan_ok:
+            # a step of few tokens: one launch, a CTA per (head, request)
+            ops.mmem_step(gated, proj, columns, self.i_bias, self.f_bias, self.norm, *states,
+                          ctx.q_start, ctx.state_slot, ctx.positions, requests, self.heads,
+                          self.dim, self.vdim, self.cap, self.q_scale, self.eps,
+                          out_scale=self.out_scale)
+        else:
+            # portions are cut into segments that run side by side (workspaces sized once, for
+            # the largest step the runtime takes)
+            n = ops.mmem_max_segments(max(ctx.runtime.max_batched_tokens, ctx.layout.t_cap),
+                                      max(ctx.runtime.max_requests, requests))
+            big, small = (n, self.heads, self.vdim, self.dim), (n, self.heads, self.dim)
+            segments = (ctx.scratch("mmem_seg_own", big, torch.float32),
+                        ctx.scratch("mmem_seg_start", big, torch.float32),
+                        ctx.scratch("mmem_seg_own_n", small, torch.float32),
+                        ctx.scratch("mmem_seg_start_n", small, torch.float32),
+                        ctx.scratch("mmem_seg_keep", (n, self.heads), torch.float32))
+            raw = ctx.scratch("mmem_raw", (cap, self.heads * self.vdim), torch.float32)[:t]
+            gates = ctx.scratch("mmem_gates", (cap, self.heads, 4), torch.float32)[:t]
+            cols = self.vdim           # value columns a CTA: halved while the GPU is not filled twice
+            while cols > 8 and self.heads * n * -(-self.vdim // cols) < 2 * self.sm_count:
+                cols = -(-cols // 2)
+            ops.mmem_scan(gated, raw, gates, proj, columns, self.i_bias, self.f_bias, self.norm,
+                          *states, ctx.q_start, ctx.state_slot, ctx.positions, ctx.seq_of_token,
+                          requests, self.heads, self.dim, self.vdim, self.cap, self.q_scale,
+                          self.eps, out_scale=self.out_scale, columns=cols, segments=segments)
         self.out.forward(ctx, gated, x, resid=x if accumulate else None)
 
 

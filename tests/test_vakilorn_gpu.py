@@ -1,0 +1,748 @@
+"""Vakilorn in the engine against the plain implementation (``plain_vakilorn``): every mechanism
+alone at the kernels' interface, then whole models of several shapes under every way of
+cutting and batching the work, in 32-bit and in bfloat16, and greedy generation through the
+package's entry point."""
+import math
+import os
+import random
+import shutil
+
+import pytest
+import torch
+
+import plain_vakilorn as P
+from helpers import Replayer, random_tokens
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def _i32(v):
+    return torch.tensor(v, dtype=torch.int32, device=DEV)
+
+
+def _steps(parts):
+    """positions, request of each token, row offsets and slots of a step made of
+    (slot, first position, tokens) parts, with one padding request behind them."""
+    pos, seq, qs, slots = [], [], [0], []
+    for b, (slot, p0, n) in enumerate(parts):
+        pos += list(range(p0, p0 + n))
+        seq += [b] * n
+        qs.append(qs[-1] + n)
+        slots.append(slot)
+    return _i32(pos), _i32(seq), _i32(qs + [qs[-1]]), _i32(slots + [-1])
+
+
+# ------------------------------------------------------------------ mechanisms, one by one
+class RecurrenceCase:
+    """The gated linear recurrence behind a stand-in for the projections' buffer."""
+
+    def __init__(self, inner, blocks, taps, seed=0):
+        self.inner, self.blocks, self.taps = inner, blocks, taps
+        self.g = torch.Generator().manual_seed(seed)
+        rn = lambda *s: torch.randn(*s, generator=self.g)
+        bw = inner // blocks
+        self.y_b, self.x_b = rn(inner) * 0.3, rn(inner) * 0.3
+        self.conv, self.conv_b = rn(inner, taps) * 0.5, rn(inner) * 0.2
+        self.ra, self.ri = rn(blocks, bw, bw) / math.sqrt(bw), rn(blocks, bw, bw) / math.sqrt(bw)
+        self.ra_b, self.ri_b = rn(blocks, bw) * 0.5, rn(blocks, bw) * 0.5
+        self.lam = rn(inner) - 2.0
+        self.state = torch.full((3, inner), 9.0, device=DEV)            # what earlier users left
+        self.inputs = torch.full((3, max(taps - 1, 0), inner), 7.0, device=DEV)
+
+    def rows(self, n):
+        return torch.randn(n, self.inner, generator=self.g), torch.randn(n, self.inner, generator=self.g)
+
+    def plain(self, y, x):
+        T = y.shape[0]
+        u = P.causal_convolution(x.double() + self.x_b.double(), self.conv.double(), self.conv_b.double())
+        ub = u.reshape(T, self.blocks, -1)
+        r = torch.sigmoid(torch.einsum("boi,tbi->tbo", self.ra.double(), ub) + self.ra_b.double()).reshape(T, -1)
+        i = torch.sigmoid(torch.einsum("boi,tbi->tbo", self.ri.double(), ub) + self.ri_b.double()).reshape(T, -1)
+        return P.gated_recurrence_states(u, r, i, self.lam.double()) * P.tanh_gelu(y.double() + self.y_b.double())
+
+    def run(self, parts, scale=1.0):
+        """parts: (slot, first position, y, x) per request of one step."""
+        from pretrained_rstr_b200.csrc import ops
+        pad = lambda n: torch.zeros(n, 8)
+        proj = torch.cat([torch.cat([pad(y.shape[0]), y, pad(y.shape[0]), x], dim=1)
+                          for _, _, y, x in parts]).to(DEV).contiguous()
+        y_col, x_col = 8, 16 + self.inner
+        pos, seq, qs, slots = _steps([(s, p0, y.shape[0]) for s, p0, y, _ in parts])
+        t = proj.shape[0]
+        u = torch.empty(t, self.inner, device=DEV)
+        a = torch.empty(t, self.inner, device=DEV)
+        out = torch.zeros(t, self.inner + 8, device=DEV)
+        dev = lambda v: v.to(DEV).contiguous()
+        decay = dev(-8.0 * torch.nn.functional.softplus(self.lam))
+        ops.lru_conv(u, proj, x_col, dev(self.x_b), dev(self.conv), dev(self.conv_b), self.inputs,
+                     seq, pos, qs, slots)
+        ops.lru_gates(a, u, dev(self.ra.transpose(1, 2)), dev(self.ri.transpose(1, 2)),
+                      dev(self.ra_b.reshape(-1)), dev(self.ri_b.reshape(-1)), decay, self.blocks)
+        ops.lru_scan(out, a, u, proj, y_col, x_col, dev(self.y_b), dev(self.x_b), self.state,
+                     self.inputs, qs, slots, pos, len(parts) + 1, out_scale=scale)
+        return out.cpu().double()[:, :self.inner]
+
+
+@pytest.mark.parametrize("inner,blocks,taps", [(48, 3, 3), (40, 1, 4), (64, 8, 1), (130, 2, 2),
+                                               (36, 36, 6), (256, 4, 4)])
+def test_linear_recurrence_kernels(inner, blocks, taps):
+    """A whole sequence at once; the same in portions down to one token (the convolution's taps
+    cross every cut) beside another request; a slot's earlier state and saved inputs are not
+    read at position 0 and are carried from then on."""
+    case = RecurrenceCase(inner, blocks, taps, seed=inner + taps)
+    n = 83
+    y, x = case.rows(n)
+    y2, x2 = case.rows(29)
+    want, want2 = case.plain(y, x), case.plain(y2, x2)
+    got = case.run([(1, 0, y, x)])
+    assert torch.allclose(got, want, atol=2e-5, rtol=1e-5)
+    at, k = 0, 0
+    cuts = [1, 2, 1, 5, 1, 1, 17, 2, 30, 3]
+    other = 0
+    pieces = []
+    while at < n:
+        m = min(cuts[k % len(cuts)], n - at)
+        k += 1
+        parts = [(2, at, y[at:at + m], x[at:at + m])]
+        if other < 29:                                     # another request rides along
+            mo = min(4, 29 - other)
+            parts.insert(0, (0, other, y2[other:other + mo], x2[other:other + mo]))
+        got = case.run(parts, scale=0.5)
+        if len(parts) == 2:
+            assert torch.allclose(got[:mo] * 2, want2[other:other + mo], atol=2e-5, rtol=1e-5)
+            other += mo
+            got = got[mo:]
+        pieces.append(got * 2)
+        at += m
+    assert torch.allclose(torch.cat(pieces), want, atol=2e-5, rtol=1e-5)
+
+
+def test_linear_recurrence_far_token_stands_out():
+    """A decay close to one keeps a token from hundreds of positions back in the state; the
+    kernels carry it through many one-token steps."""
+    case = RecurrenceCase(32, 2, 2, seed=5)
+    case.lam = torch.full((32,), -9.0)                      # a = exp(-8 r softplus(-9)): 0.999...
+    n = 400
+    y, x = case.rows(n)
+    x[3] *= 40.0
+    want = case.plain(y, x)
+    assert float(want[n - 1].abs().max()) > 1.0            # the far token still matters
+    got = [case.run([(1, 0, y[:5], x[:5])])]
+    for t in range(5, n):
+        got.append(case.run([(1, t, y[t:t + 1], x[t:t + 1])]))
+    assert torch.allclose(torch.cat(got), want, atol=1e-4, rtol=1e-4)
+
+
+class MemoryCase:
+    """The matrix memory behind a stand-in for the projections' buffer."""
+
+    def __init__(self, heads, dim, vdim, cap, seed=0):
+        self.heads, self.dim, self.vdim, self.cap = heads, dim, vdim, cap
+        self.g = torch.Generator().manual_seed(seed)
+        rn = lambda *s: torch.randn(*s, generator=self.g)
+        self.i_b, self.f_b = rn(heads), rn(heads) + 2.0
+        self.norm_w = 1.0 + 0.1 * rn(heads * vdim)
+        self.s = torch.full((3, heads, vdim, dim), 9.0, device=DEV)     # what earlier users left
+        self.n = torch.full((3, heads, dim), 5.0, device=DEV)
+        self.m = torch.full((3, heads), 3.0, device=DEV)
+
+    def rows(self, n):
+        r = lambda *s: torch.randn(n, *s, generator=self.g)
+        return (r(self.heads, self.dim), r(self.heads, self.dim), r(self.heads, self.vdim),
+                r(self.heads) * 3, r(self.heads) * 3, r(self.heads, self.vdim))
+
+    def plain(self, q, k, v, ig, fg, gate, eps):
+        cap = self.cap
+        i = cap * torch.tanh((ig.double() + self.i_b.double()) / cap)
+        f = torch.nn.functional.logsigmoid(cap * torch.tanh((fg.double() + self.f_b.double()) / cap))
+        o = P.matrix_memory_outputs(q.double() * self.dim ** -0.5, k.double(), v.double(), i, f)
+        return P.unit_rms(o, eps) * self.norm_w.double().reshape(self.heads, self.vdim) * torch.sigmoid(gate.double())
+
+    def run(self, parts, eps, mode, scale=1.0):
+        """parts: (slot, first position, q, k, v, i, f, gate) per request of one step; ``mode``:
+        "step" (one launch), "scan" (a CTA per request's portion) or "segments"."""
+        from pretrained_rstr_b200.csrc import ops
+        hd, d, vd = self.heads, self.dim, self.vdim
+        rows = []
+        for _, _, q, k, v, ig, fg, gate in parts:
+            n = q.shape[0]
+            pad = torch.zeros(n, 4)
+            rows.append(torch.cat([pad, q.reshape(n, -1), k.reshape(n, -1), pad, v.reshape(n, -1),
+                                   gate.reshape(n, -1), pad, ig, torch.zeros(n, 8 - hd % 8), fg,
+                                   torch.zeros(n, 8)], dim=1))
+        proj = torch.cat(rows).to(DEV)
+        proj = torch.cat([proj, torch.zeros(proj.shape[0], -proj.shape[1] % 4, device=DEV)], dim=1).contiguous()
+        q_col, k_col = 4, 4 + hd * d
+        v_col = 8 + 2 * hd * d
+        g_col = v_col + hd * vd
+        i_col = g_col + hd * vd + 4
+        f_col = i_col + hd + 8 - hd % 8
+        cols = (q_col, k_col, v_col, i_col, f_col, g_col)
+        pos, seq, qs, slots = _steps([(p[0], p[1], p[2].shape[0]) for p in parts])
+        t = proj.shape[0]
+        out = torch.zeros(t, hd * vd + 8, device=DEV)
+        dev = lambda x: x.to(DEV).contiguous()
+        common = (dev(self.i_b), dev(self.f_b), dev(self.norm_w), self.s, self.n, self.m, qs, slots, pos)
+        if mode == "step":
+            ops.mmem_step(out, proj, cols, *common, len(parts) + 1, hd, d, vd, self.cap,
+                          d ** -0.5, eps, out_scale=scale)
+        else:
+            segments = None
+            if mode == "segments":
+                n = ops.mmem_max_segments(t, len(parts) + 1) + 1
+                full = lambda *s: torch.full(s, 3.0, device=DEV)
+                segments = (full(n, hd, vd, d), full(n, hd, vd, d), full(n, hd, d), full(n, hd, d), full(n, hd))
+            raw = torch.full((t, hd * vd), 77.0, device=DEV)
+            gates = torch.full((t, hd, 4), 77.0, device=DEV)
+            ops.mmem_scan(out, raw, gates, proj, cols, *common, seq, len(parts) + 1, hd, d, vd,
+                          self.cap, d ** -0.5, eps, out_scale=scale,
+                          columns=max(1, vd // 2) if vd > 8 else vd, segments=segments)
+        return out.cpu().double()[:, :hd * vd].reshape(t, hd, vd)
+
+
+@pytest.mark.parametrize("mode", ["step", "scan", "segments"])
+@pytest.mark.parametrize("heads,dim,vdim,cap", [(3, 8, 24, 6.0), (2, 64, 64, 15.0), (1, 40, 136, 4.0),
+                                                (2, 160, 16, 10.0), (5, 3, 5, 2.0), (1, 16, 16, 30.0)])
+def test_matrix_memory_kernels(heads, dim, vdim, cap, mode):
+    """A whole sequence at once, in portions down to one token and longer than a segment, beside
+    another request; the slot's earlier state, normaliser and maximum are not read at position
+    0 and are carried from then on; each way the recurrence runs."""
+    case = MemoryCase(heads, dim, vdim, cap, seed=dim + vdim)
+    eps = 1e-5
+    n = 150
+    a, b = case.rows(n), case.rows(31)
+    want, want2 = case.plain(*a, eps), case.plain(*b, eps)
+    tol = dict(atol=5e-5, rtol=2e-4)
+    got = case.run([(1, 0, *a)], eps, mode)
+    assert torch.allclose(got, want, **tol)
+    cuts = [1, 2, 70, 1, 1, 5, 66, 2, 1, 1]
+    at, k, other, pieces = 0, 0, 0, []
+    while at < n:
+        m = min(cuts[k % len(cuts)], n - at)
+        k += 1
+        parts = [(2, at, *(x[at:at + m] for x in a))]
+        mo = 0
+        if other < 31:
+            mo = min(3, 31 - other)
+            parts.insert(0, (0, other, *(x[other:other + mo] for x in b)))
+        got = case.run(parts, eps, mode, scale=0.5) * 2
+        if mo:
+            assert torch.allclose(got[:mo], want2[other:other + mo], **tol)
+            other += mo
+        pieces.append(got[mo:])
+        at += m
+    assert torch.allclose(torch.cat(pieces), want, **tol)
+
+
+def test_matrix_memory_maximum_starts_at_zero():
+    """Input gates far below zero: the running maximum stays at its start, 0, and the outputs
+    are small instead of being rescaled to unit size; a maximum that started at minus infinity
+    would give other numbers."""
+    case = MemoryCase(2, 8, 8, 50.0, seed=3)
+    case.i_b = torch.full((2,), -20.0)
+    a = list(case.rows(6))
+    a[3] = a[3] * 0.1
+    want = case.plain(*a, 1e-6)
+    for mode in ("step", "scan"):
+        got = case.run([(0, 0, *a)], 1e-6, mode)
+        assert torch.allclose(got, want, atol=1e-6, rtol=1e-4)
+
+
+class SinkCase:
+    """Attention over cache rows [k | v] with a sink per head and a gate per value coordinate."""
+
+    def __init__(self, heads, kv_heads, dim, vdim, seed=0, page_size=16, dtype=torch.float32):
+        self.heads, self.kv_heads, self.dim, self.vdim = heads, kv_heads, dim, vdim
+        self.page_size, self.dtype = page_size, dtype
+        self.g = torch.Generator().manual_seed(seed)
+        self.sinks = torch.randn(heads, generator=self.g) * 2
+
+    def run(self, n_keys, queries, window, scale, kind, gate_per_value=True, sinks=True):
+        """``queries``: positions of the step's tokens (one request holding n_keys tokens)."""
+        from pretrained_rstr_b200.csrc import ops
+        H, G, D, V, ps = self.heads, self.kv_heads, self.dim, self.vdim, self.page_size
+        rn = lambda *s: torch.randn(*s, generator=self.g)
+        k, v = rn(n_keys, G, D), rn(n_keys, G, V)
+        q = rn(n_keys, H, D)
+        gate = rn(n_keys, H * V if gate_per_value else H)
+        k, v = k.to(self.dtype).float(), v.to(self.dtype).float()
+        n_pages = -(-n_keys // ps)
+        order = list(range(n_pages + 3))
+        random.Random(n_keys).shuffle(order)
+        table = order[:n_pages]
+        cache = torch.full((n_pages + 3, G, ps, D + V), 55.0)
+        for j in range(n_keys):
+            cache[table[j // ps], :, j % ps] = torch.cat([k[j], v[j]], dim=-1)
+        cache = cache.to(self.dtype).to(DEV)
+        bt = _i32([table + [-1] * 2])
+        t = len(queries)
+        out = torch.zeros(t, H * V + 8, dtype=self.dtype, device=DEV)
+        status = torch.zeros(4, dtype=torch.int32, device=DEV)
+        gt = torch.cat([torch.zeros(t, 8), gate[queries]], dim=1).to(DEV)
+        ops.wattn(out, q[queries].reshape(t, -1).to(DEV).contiguous(), cache, bt, _i32([0] * t),
+                  _i32(queries), H, D, V, window, 0, scale, gate=gt[:, 8:], status=status,
+                  tile_rows=ops.wattn_tile_rows(H, G, D, V) if kind == "tile" else 0,
+                  single=kind == "single", sinks=self.sinks.to(DEV) if sinks else None,
+                  gate_per_value=gate_per_value)
+        assert int(status[0]) == 0, status.tolist()
+        want = P.masked_softmax_attention(q.double(), k.double(), v.double(), scale,
+                                          sink=self.sinks.double() if sinks else None,
+                                          window=window or None)
+        g = torch.sigmoid(gate.double())
+        want = want * (g.reshape(n_keys, H, V) if gate_per_value else g[:, :, None])
+        return out.float().cpu().double()[:, :H * V].reshape(t, H, V), want[queries]
+
+
+@pytest.mark.parametrize("kind", ["tile", "single", "any"])
+@pytest.mark.parametrize("heads,kv_heads,dim,vdim", [(4, 2, 16, 24), (6, 1, 40, 8), (3, 3, 24, 72), (2, 1, 8, 136)])
+def test_attention_sink_and_value_gate(heads, kv_heads, dim, vdim, kind):
+    """The sink joins the denominator once, unscaled, whatever the number of key blocks and
+    warps that are joined; the gate acts per value coordinate.  Prompt rows and single tokens,
+    with and without a window, in both cache types."""
+    from pretrained_rstr_b200.csrc import ops
+    if kind == "tile" and ops.wattn_tile_rows(heads, kv_heads, dim, vdim) == 0:
+        pytest.skip("the tiled kernel does not take these sizes")
+    if kind == "single" and not ops.wattn_single_supports(heads, kv_heads, dim, vdim):
+        pytest.skip("the single-token kernel does not take these sizes")
+    for dtype, tol in ((torch.float32, 2e-5), (torch.bfloat16, 2e-2)):
+        case = SinkCase(heads, kv_heads, dim, vdim, seed=dim, dtype=dtype)
+        for n_keys, window in ((1, 0), (45, 0), (300, 0), (300, 70)):
+            queries = [n_keys - 1] if kind == "single" else sorted({0, n_keys // 2, n_keys - 1})
+            if kind == "tile":
+                queries = list(range(max(0, n_keys - 9), n_keys))
+            for per_value in (True, False):
+                got, want = case.run(n_keys, queries, window, 0.3, kind, gate_per_value=per_value)
+                assert torch.allclose(got, want, atol=tol, rtol=tol), (n_keys, window, per_value)
+
+
+def test_sink_takes_weight_from_the_keys():
+    """A large sink leaves the keys almost no weight, a very small one changes nothing: the
+    result scales as the closed form says."""
+    case = SinkCase(2, 1, 8, 8, seed=1)
+    case.sinks = torch.tensor([30.0, -30.0])
+    got, want = case.run(20, [19], 0, 0.5, "any", gate_per_value=False)
+    assert torch.allclose(got, want, atol=1e-6)
+    assert float(got[0, 0].abs().max()) < 1e-6 < float(got[0, 1].abs().max())
+
+
+@pytest.mark.parametrize("mode", ["head", "head_after"])
+def test_prepare_norms_per_head(mode):
+    """Queries and keys as the attention reads them: biases join first; a norm per head with a
+    shared weight before the rotation, or without a weight after it; frequencies divided by a
+    constant; values with their bias in the cache row."""
+    from pretrained_rstr_b200.csrc import ops
+    from pretrained_rstr_b200.parts.positions_rotary import rotary_frequencies
+    H, G, D, V, rot, ps, eps = 5, 1, 24, 10, 16, 8, 1e-4
+    g = torch.Generator().manual_seed(11)
+    rn = lambda *s: torch.randn(*s, generator=g)
+    n = 7
+    pos = [0, 1, 9, 250, 251, 4000, 33]
+    q, k, v = rn(n, H * D), rn(n, G * D), rn(n, G * V)
+    bq, bk, bv = (rn(H * D), rn(G * D), rn(G * V)) if mode == "head" else (None, None, None)
+    wq, wk = (1 + 0.2 * rn(D), 1 + 0.2 * rn(D)) if mode == "head" else (None, None)
+    factor = 1.0 if mode == "head" else 3.5
+    proj = torch.cat([torch.zeros(n, 8), q, k, torch.zeros(n, 8), v], dim=1).to(DEV).contiguous()
+    q_col, k_col, v_col = 8, 8 + H * D, 16 + H * D + G * D
+    cache = torch.zeros(5, G, ps, D + V, device=DEV)
+    slots = [3, 4, 9, 20, 21, 39, 30]
+    q_out = torch.empty(n, H * D, device=DEV)
+    dev = lambda t: None if t is None else t.to(DEV).contiguous()
+    freq = rotary_frequencies(500.0, rot, DEV, divide_by=factor)
+    ops.wattn_prepare(q_out, cache, proj, q_col, k_col, v_col, dev(wq), dev(wk), _i32(slots),
+                      _i32(pos), freq, H, G, D, V, rot, eps, 0.0, 0, head_norm=
+                      "before" if mode == "head" else "after", biases=None if bq is None else (dev(bq), dev(bk), dev(bv)))
+    positions = torch.tensor(pos)
+    f = P.plain_frequencies(500.0, rot) / factor
+    qd, kd = q.double().reshape(n, H, D), k.double().reshape(n, G, D)
+    if mode == "head":
+        qd = P.unit_rms(qd + bq.double().reshape(H, D), eps) * wq.double()
+        kd = P.unit_rms(kd + bk.double().reshape(G, D), eps) * wk.double()
+        qd, kd = P.turn(qd, positions, f, rot, "half"), P.turn(kd, positions, f, rot, "half")
+        vd = v.double() + bv.double()
+    else:
+        qd, kd = P.turn(qd, positions, f, rot, "half"), P.turn(kd, positions, f, rot, "half")
+        qd, kd = P.unit_rms(qd, eps), P.unit_rms(kd, eps)
+        vd = v.double()
+    assert torch.allclose(q_out.cpu().double().reshape(n, H, D), qd, atol=5e-4, rtol=1e-4)
+    for i, s in enumerate(slots):
+        row = cache[s // ps, :, s % ps].cpu().double()
+        assert torch.allclose(row[:, :D], kd[i], atol=5e-4, rtol=1e-4)
+        assert torch.allclose(row[:, D:], vd[i].reshape(G, V), atol=1e-6)
+
+
+def test_branch_norm_and_scaled_pair_embedding():
+    """x + norm(y) with a weight stored around zero, in place, with the copy in the activation
+    type; the token's row times a constant plus the pair's row."""
+    from pretrained_rstr_b200.csrc import ops
+    g = torch.Generator().manual_seed(2)
+    x, y, w = torch.randn(9, 40, generator=g), torch.randn(9, 40, generator=g) * 3, torch.randn(40, generator=g) * 0.1
+    want = x.double() + P.offset_norm(y.double(), w.double(), 1e-5)
+    xd, copy = x.to(DEV), torch.empty(9, 40, dtype=torch.bfloat16, device=DEV)
+    ops.rms_norm(xd, out=copy, x_out=xd, y=y.to(DEV), weight=(1.0 + w).to(DEV), eps=1e-5, branch_only=True)
+    assert torch.allclose(xd.cpu().double(), want, atol=1e-5)
+    assert torch.allclose(copy.float().cpu().double(), want, atol=3e-2)
+    table, pairs = torch.randn(30, 16, generator=g), torch.randn(12, 16, generator=g)
+    tokens = [4, 29, 0, 7, 7, 3]
+    out = torch.empty(6, 16, device=DEV)
+    prev = _i32([99, 5, 99])
+    pos, seq, qs, slots = _steps([(1, 3, 2), (2, 0, 4)])
+    ops.embed_pair(out, _i32(tokens), pos, seq, qs, slots, prev, table.to(DEV), pairs.to(DEV), 11, 13, 3,
+                   None, scale=2.5)
+    befores = [5, 4, None, 0, 7, 7]
+    for t, (tok, before) in enumerate(zip(tokens, befores)):
+        row = 11 if before is None else (before * 13 + tok * 3) % 11
+        assert torch.allclose(out[t].cpu(), table[tok] * 2.5 + pairs[row], atol=1e-6)
+    assert prev.cpu().tolist() == [99, 29, 3]
+
+
+def test_yarn_frequencies_and_interleaved_reordering():
+    from pretrained_rstr_b200.parts.positions_rotary import yarn_frequencies
+    for base, dims, factor, original, fast, slow in ((10000.0, 16, 8.0, 256, 32.0, 1.0),
+                                                    (500000.0, 64, 4.0, 4096, 16.0, 2.0), (77.0, 2, 1.5, 10, 3.0, 0.5)):
+        got, mag = yarn_frequencies(base, dims, factor, original, fast, slow, "cpu")
+        want, wmag = P.yarn(base, dims, factor, original, fast, slow)
+        assert torch.allclose(got.double(), want, rtol=1e-6) and abs(mag - wmag) < 1e-12
+    # interleaved pairs reordered to halves: dot products are unchanged
+    g = torch.Generator().manual_seed(0)
+    a, b = torch.randn(3, 1, 12, generator=g).double(), torch.randn(3, 1, 12, generator=g).double()
+    pos, f = torch.tensor([0, 5, 91]), P.plain_frequencies(100.0, 8)
+    order = [0, 2, 4, 6, 1, 3, 5, 7, 8, 9, 10, 11]
+    inter = (P.turn(a, pos, f, 8, "interleaved") * P.turn(b, pos, f, 8, "interleaved")).sum(-1)
+    half = (P.turn(a[..., order], pos, f, 8, "half") * P.turn(b[..., order], pos, f, 8, "half")).sum(-1)
+    assert torch.allclose(inter, half, atol=1e-12)
+
+
+# ------------------------------------------------------------------------ whole models
+def _left(heads, kv_heads, dim, vdim, rot_dims=None, base=10000.0, factor=None, scale=None):
+    rot = {"base": base, "dims": dim if rot_dims is None else rot_dims}
+    if factor is not None:
+        rot["scaling"] = {"factor": factor}
+    return {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim,
+            "scale": 1.0 / math.sqrt(dim) if scale is None else scale, "rot": rot}
+
+
+def _dense(ff, limit):
+    return {"kind": "dense", "ff": ff, "limit": limit}
+
+
+def _rec(left, inner, blocks, taps, mlp, ls=0.8, rs=0.6, **extra):
+    return {"type": "parallel", "mixer": {"left": left, "right": {"width": inner, "blocks": blocks, "conv": taps},
+                                          "left_scale": ls, "right_scale": rs}, "mlp": mlp, **extra}
+
+
+def _mem(left, heads, dim, vdim, cap, mlp, ls=1.1, rs=0.7, **extra):
+    return {"type": "parallel_2", "mixer": {"left": left, "right": {"heads": heads, "dim": dim, "vdim": vdim,
+                                                                    "gate_cap": cap},
+                                            "left_scale": ls, "right_scale": rs}, "mlp": mlp, **extra}
+
+
+def _lat(heads, dim, rot_dim, vdim, rank, window, mlp, base=10000.0, factor=8.0, original=256, fast=32.0,
+         slow=1.0, scale=None, **extra):
+    return {"type": "latent_attention",
+            "mixer": {"heads": heads, "dim": dim, "rot_dim": rot_dim, "vdim": vdim, "kv_rank": rank,
+                      "scale": 1.0 / math.sqrt(dim + rot_dim) if scale is None else scale,
+                      "mask": {"size": window},
+                      "rot": {"base": base, "dims": rot_dim, "scaling": {"factor": factor, "original": original,
+                                                                         "fast": fast, "slow": slow}}},
+            "mlp": mlp, **extra}
+
+
+def _model(vocab, width, layers, buckets, mul_prev, mul_cur, scale, eps=1e-6):
+    return {"architecture": "Vakilorn", "vocab": vocab, "width": width, "norm": {"eps": eps},
+            "embedding": {"scale": scale, "bigram": {"buckets": buckets, "mul_prev": mul_prev, "mul_cur": mul_cur}},
+            "layers": layers}
+
+
+_A0 = _rec(_left(4, 2, 16, 24, rot_dims=8), 48, 3, 3, _dense(96, 1.2))
+SHAPE_A = _model(300, 64, [
+    _A0,
+    _lat(2, 24, 8, 16, 40, 21, _dense(72, 0.9), original=64, factor=3.0, fast=16.0),
+    _mem(_left(2, 1, 24, 8, factor=2.5), 3, 8, 24, 6.0, None),
+    {**_A0, "weights_of": 0}], 97, 31, 5, 8.0)
+# other sizes: as many key/value heads as heads, one block, one tap, heads the tensor-core
+# kernels do not take, a window wider than several pages, a layer that runs a LATER layer's
+# tensors, and a model without pair rows' usual sizes
+_B3 = _lat(3, 40, 12, 56, 72, 150, _dense(200, 5.0), base=300.0, factor=2.0, original=32, fast=8.0, slow=2.0,
+           scale=0.2)
+SHAPE_B = _model(515, 128, [
+    _mem(_left(3, 3, 40, 56, rot_dims=0), 1, 40, 136, 30.0, _dense(72, 2.0), ls=0.5, rs=1.5),
+    {**_B3, "weights_of": 3},
+    _rec(_left(6, 2, 8, 136, rot_dims=8, base=77.0), 40, 1, 1, None, ls=1.3, rs=0.4),
+    _B3,
+    _lat(4, 16, 32, 16, 64, 300, _dense(64, 1.0), original=4096, factor=16.0)], 2, 7, 7, 11.3, eps=1e-5)
+SHAPE_C = _model(200, 48, [
+    _lat(1, 16, 16, 16, 16, 1, _dense(56, 3.0)),
+    _rec(_left(3, 1, 32, 48, rot_dims=16), 96, 4, 4, _dense(56, 0.7), ls=1.0, rs=1.0),
+    _mem(_left(1, 1, 16, 16, factor=1.0), 2, 64, 64, 12.0, _dense(40, 4.0))], 1000, 1, 0, 1.0)
+SHAPES = {"A": (SHAPE_A, 41), "B": (SHAPE_B, 42), "C": (SHAPE_C, 43)}
+CASES = [(name, dtype) for name in SHAPES for dtype in ("float32", "bfloat16")]
+# Relative difference of a row of logits (see ``row_error``).  float32: summation order only.
+# bfloat16: the stream's copy, the mixers' results and the cache rows are rounded to 8 bits of
+# mantissa before every product, and every branch's result is brought to unit size before it
+# joins the stream, so a branch's rounding reaches the stream undamped: about one percent a
+# row at these widths, with a tail of a few percent among hundreds of rows.  The largest row
+# and the middle one are both bounded.
+TOL = {"float32": 2e-4, "bfloat16": 6e-2}
+TOL_MEDIAN = {"float32": 5e-5, "bfloat16": 2e-2}
+
+
+@pytest.fixture(scope="module")
+def folders(tmp_path_factory):
+    from pretrained_rstr_b200.config.registry import lookup
+    from pretrained_rstr_b200.weights import make_random_model
+    out = {}
+    for name, (raw, seed) in SHAPES.items():
+        cfg = lookup(raw).config_class.from_dict(raw)
+        for dtype in ("float32", "bfloat16"):
+            path = str(tmp_path_factory.mktemp(f"vakilorn{name}_{dtype}"))
+            make_random_model(path, cfg, seed, torch.bfloat16 if dtype == "bfloat16" else torch.float32)
+            out[(name, dtype)] = path
+    return out
+
+
+def _oracle(folder, prompts):
+    cfg, tensors = P.read_folder(folder)
+    return {rid: P.forward(list(ids), tensors, cfg).to(torch.float32) for rid, ids in prompts.items()}
+
+
+def row_error(row, ref) -> float:
+    """Root mean square of the difference (its mean taken off) over that of the reference row."""
+    d = row.double() - ref.double()
+    d = d - d.mean()
+    r = ref.double() - ref.double().mean()
+    return float(d.pow(2).mean().sqrt() / r.pow(2).mean().sqrt())
+
+
+def compare(rows, oracle, tol):
+    assert rows
+    errs = []
+    for (rid, pos), row in sorted(rows.items()):
+        err = row_error(row, oracle[rid][pos])
+        assert err == err, f"NaN at request {rid} position {pos}"
+        assert err <= tol, (f"request {rid} position {pos} (page offset {pos % 64}): relative "
+                            f"difference {err:.3e} > {tol:.1e}")
+        errs.append(err)
+    errs.sort()
+    middle = errs[len(errs) // 2]
+    print(f"rows {len(errs)}: median {middle:.2e}, largest {errs[-1]:.2e}")
+    bound = TOL_MEDIAN["float32" if tol == TOL["float32"] else "bfloat16"]
+    assert len(errs) < 8 or middle <= bound, f"the middle row differs by {middle:.3e} > {bound:.1e}"
+    return errs[-1]
+
+
+def _prompts(name, lengths, salt=0):
+    raw, seed = SHAPES[name]
+    return {f"r{i}": random_tokens(n, raw["vocab"], 1000 * seed + salt + i) for i, n in enumerate(lengths)}
+
+
+def test_layers_one_by_one(folders):
+    """The stream after every layer run (a layer that runs another's tensors counts) in 32-bit."""
+    from pretrained_rstr_b200.engine.batch import Entry
+    from pretrained_rstr_b200.engine.loading import load_model
+    for name in SHAPES:
+        folder = folders[(name, "float32")]
+        cfg, tensors = P.read_folder(folder)
+        ids = _prompts(name, [37])["r0"]
+        taps = []
+        P.forward(ids, tensors, cfg, taps=taps)
+        lm = load_model(folder, dtype="float32", page_size=64, max_batched_tokens=64, max_requests=2,
+                        max_tokens=128)
+        seen = []
+        lm.model.tap = lambda i, x: seen.append(x[:len(ids)].detach().cpu().double().clone())
+        lm.cache.open("a")
+        lm.runner.step([Entry("a", ids, [0])])
+        lm.runner.check_status()
+        assert len(seen) == len(taps) == len(cfg["layers"])
+        for i, (got, want) in enumerate(zip(seen, taps)):
+            assert float((got - want).abs().max()) < 2e-4 * float(want.abs().max()), f"{name}: layer run {i}"
+
+
+@pytest.mark.parametrize("name,dtype", CASES)
+def test_whole_prompts_decode_and_portions(folders, name, dtype):
+    """Whole prompts in one step; the last tokens one by one (across windows' edges); portions of
+    several sizes, down to two tokens, cut inside pages, windows and segments."""
+    folder = folders[(name, dtype)]
+    prompts = _prompts(name, [1, 2, 23, 64, 65, 150, 330])
+    oracle = _oracle(folder, prompts)
+    rp = Replayer(folder, dtype, max_tokens=512)
+    for rid, ids in prompts.items():
+        rp.step([(rid, ids, list(range(len(ids))))], end=[rid])
+    compare(rp.rows, oracle, TOL[dtype])
+    rp.rows.clear()
+    for rid, ids in prompts.items():
+        head = max(1, len(ids) - 40)
+        rp.step([(rid, ids[:head], [head - 1])], end=[rid] if head == len(ids) else [])
+        for i in range(head, len(ids)):
+            rp.step([(rid, ids[i:i + 1], [0])], end=[rid] if i == len(ids) - 1 else [])
+    compare(rp.rows, oracle, TOL[dtype])
+    rp.rows.clear()
+    sizes = [3, 2, 19, 2, 2, 40, 5, 64, 2, 66, 2, 130]
+    for r, (rid, ids) in enumerate(prompts.items()):
+        at, k = 0, r
+        while at < len(ids):
+            n = min(sizes[k % len(sizes)], len(ids) - at)
+            k += 1
+            rp.step([(rid, ids[at:at + n], list(range(n)))], end=[rid] if at + n >= len(ids) else [])
+            at += n
+    compare(rp.rows, oracle, TOL[dtype])
+
+
+@pytest.mark.parametrize("name,dtype", [("A", "float32"), ("B", "bfloat16"), ("B", "float32"), ("C", "float32")])
+def test_long_decode(folders, name, dtype):
+    """Two tokens of prompt and some 340 decoded one by one: every window and several pages'
+    borders are passed by single tokens, the states are carried all the way."""
+    folder = folders[(name, dtype)]
+    prompts = _prompts(name, [342], salt=50)
+    oracle = _oracle(folder, prompts)
+    rp = Replayer(folder, dtype, max_tokens=384)
+    ids = prompts["r0"]
+    rp.step([("r0", ids[:2], [0, 1])])
+    for i in range(2, len(ids)):
+        rp.step([("r0", ids[i:i + 1], [0])])
+    compare(rp.rows, oracle, TOL[dtype])
+
+
+@pytest.mark.parametrize("name,dtype", CASES)
+def test_mixed_batches_with_reuse(folders, name, dtype):
+    """Up to four live requests of unequal lengths, portions of some beside single tokens of
+    others, some left out of a step, in a pool so small that pages and state slots of finished
+    requests are used again: every row as if its request ran alone."""
+    folder = folders[(name, dtype)]
+    lengths = [130, 64, 250, 9, 33, 200, 1, 120, 2, 77]
+    prompts = _prompts(name, lengths, salt=90)
+    oracle = _oracle(folder, prompts)
+    biggest = sorted((-(-n // 64) * 64 for n in lengths), reverse=True)
+    rp = Replayer(folder, dtype, max_tokens=sum(biggest[:4]))
+    rng = random.Random(5)
+    waiting, live, slots_seen = list(prompts), {}, []
+    while waiting or live:
+        while waiting and len(live) < 4:
+            live[waiting.pop(0)] = 0
+        entries, end = [], []
+        for rid in list(live):
+            ids, at = prompts[rid], live[rid]
+            left = len(ids) - at
+            if rng.random() < 0.25 and len(live) > 1:
+                continue                                   # left out of this step
+            if left > 20 and at < len(ids) - 12:
+                n = min(left - 12, rng.choice([2, 3, 8, 21, 64, 70]))
+            else:
+                n = 1
+            entries.append((rid, ids[at:at + n], list(range(n))))
+            live[rid] = at + n
+            if live[rid] == len(ids):
+                end.append(rid)
+                del live[rid]
+        if entries:
+            rp.step(entries, end=end)
+            slots_seen += [rp.lm.cache.slot(r) for r in live if r in rp.pos]
+    cache = rp.lm.cache
+    assert cache.stats["allocated"] > cache.allocators[0].num_pages
+    assert cache.free_pages(0) == cache.allocators[0].num_pages
+    assert len(prompts) > 4 >= len(set(slots_seen))          # state slots were used again
+    compare(rp.rows, oracle, TOL[dtype])
+
+
+def test_marked_token_at_every_edge(folders, tmp_path):
+    """A model whose keys are made to matter: one token id whose table row is large makes its
+    key, value and state contribution stand out wherever it sits.  It is put just inside and
+    just outside the latent attention's window, at the sequence's start and far back, in a
+    prompt and while decoding; a window one token off, a lost first token or a lost state moves
+    the logits far beyond the tolerance."""
+    from pretrained_rstr_b200.weights.safetensors_io import save_file
+    folder = folders[("A", "float32")]
+    cfg, tensors = P.read_folder(folder)
+    tensors = {k: v.clone() for k, v in tensors.items()}
+    marked = 7
+    tensors["embed"][marked] *= 6.0
+    path = str(tmp_path / "marked")
+    os.makedirs(path)
+    shutil.copy(folder + "/config.json", path + "/config.json")
+    save_file({k: (v.float() if v.dtype == torch.float64 else v) for k, v in tensors.items()},
+              path + "/model.safetensors")
+    cfg, tensors = P.read_folder(path)
+    n, w = 120, 21
+    clean = lambda seed: [t if t != marked else marked + 1 for t in random_tokens(n, cfg["vocab"], seed)]
+    prompts = {}
+    for delta in (0, 1):                                         # just inside, just outside
+        ids = clean(400)
+        ids[n - w + (1 - delta) - 1] = marked                     # distance w - 1 + delta from the end
+        prompts[f"w_{delta}"] = ids
+    for spot in (0, 1, 63, 64):                                  # the first tokens, a page's border
+        ids = clean(500 + spot)
+        ids[spot] = marked
+        prompts[f"s{spot}"] = ids
+    oracle = {rid: P.forward(ids, tensors, cfg).to(torch.float32) for rid, ids in prompts.items()}
+    assert row_error(oracle["w_0"][n - 1], oracle["w_1"][n - 1]) > 20 * TOL["float32"]
+    rp = Replayer(path, "float32", max_tokens=4 * 128)
+    for rid, ids in prompts.items():                             # in a prompt
+        rp.step([(rid, ids, [n - 2, n - 1])], end=[rid])
+    compare(rp.rows, oracle, TOL["float32"])
+    rp.rows.clear()
+    for rid, ids in prompts.items():                             # decoding over the edge
+        rp.step([(rid, ids[:n - 45], [])])
+        for i in range(n - 45, n):
+            rp.step([(rid, ids[i:i + 1], [0])], end=[rid] if i == n - 1 else [])
+    compare(rp.rows, oracle, TOL["float32"])
+
+
+@pytest.mark.parametrize("name,dtype", [("A", "float32"), ("A", "bfloat16"), ("C", "float32")])
+def test_greedy_generation_entry_point(folders, name, dtype):
+    """``load_lm`` / ``generate_ids`` / ``generate_batch``: the scheduler's portions, batches
+    and the steps launched ahead of their token ids choose the plain implementation's tokens."""
+    from pretrained_rstr_b200 import generate_batch, generate_ids, load_lm
+    folder = folders[(name, dtype)]
+    cfg, tensors = P.read_folder(folder)
+    m = load_lm(folder, gpu=True, dtype=dtype, max_lanes=3, max_batched_tokens=128,
+                prefill_chunk=32, maxpos=256)
+    prompts = list(_prompts(name, [1, 9, 33, 70, 130], salt=200).values())
+    n_new = 10
+
+    def agree(prompt, got):
+        want = P.greedy(prompt, n_new, tensors, cfg)
+        for i, (a, b) in enumerate(zip(got, want)):
+            if a != b:
+                row = P.forward(list(prompt) + want[:i], tensors, cfg)[-1]
+                gap = abs(float(row[a] - row[b]))
+                assert dtype == "bfloat16" and gap < 0.1, \
+                    f"token {i} is {a}, plain says {b} (logit gap {gap:.3g})"
+                return
+        assert len(got) == len(want)
+
+    agree(prompts[1], generate_ids(m, prompts[1], n_new))
+    for p, got in zip(prompts, generate_batch(m, prompts, n_new)):
+        agree(p, got)
+    cache = m.engine.lm.cache
+    assert not cache.requests
+    cache.check()
+
+
+def test_replay_as_a_program(folders, tmp_path):
+    """``bin/trace_run`` on a Vakilorn folder: the model class comes from config.json; logits of a
+    replayed trace match the plain ones."""
+    import json
+    import subprocess
+
+    import numpy as np
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    folder = folders[("A", "float32")]
+    cfg, tensors = P.read_folder(folder)
+    ids = random_tokens(40, cfg["vocab"], 77)
+    steps = [{"step": 0, "entries": [{"id": "a", "tokens": ids[:30], "want": [0, 29]}], "end": []},
+             {"step": 1, "entries": [{"id": "a", "tokens": ids[30:32], "want": []},
+                                     {"id": "b", "tokens": ids[:3], "want": [2]}], "end": ["b"]},
+             {"step": 2, "entries": [{"id": "a", "tokens": ids[32:], "want": [7]}], "end": ["a"]}]
+    out = tmp_path / "out"
+    proc = subprocess.run([os.path.join(root, "bin", "trace_run"), "--model", folder, "--dtype",
+                           "float32", "--out", str(out), "--max-tokens", "128"],
+                          input="\n".join(json.dumps(s) for s in steps) + "\n", text=True,
+                          capture_output=True, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    assert [l for l in proc.stdout.splitlines() if l.startswith("done")] == ["done 0", "done 1", "done 2"]
+    want = P.forward(ids, tensors, cfg).to(torch.float32)
+    got0 = torch.from_numpy(np.fromfile(out / "0.f32", dtype="<f4").reshape(2, -1).copy())
+    got1 = torch.from_numpy(np.fromfile(out / "1.f32", dtype="<f4").reshape(1, -1).copy())
+    got2 = torch.from_numpy(np.fromfile(out / "2.f32", dtype="<f4").reshape(1, -1).copy())
+    for row, ref in ((got0[0], want[0]), (got0[1], want[29]), (got1[0], want[2]), (got2[0], want[39])):
+        assert row_error(row, ref) < TOL["float32"]
