@@ -278,12 +278,16 @@ def embed(W, cfg: dict, tokens: List[int]) -> torch.Tensor:
 
 
 def forward(tokens: List[int], W: Dict[str, torch.Tensor], cfg: dict,
-            taps: Optional[list] = None) -> torch.Tensor:
-    """Logits [T, vocab] of one sequence; ``taps`` collects the stream after every layer."""
+            taps: Optional[list] = None, rounded_stream: bool = False) -> torch.Tensor:
+    """Logits [T, vocab] of one sequence; ``taps`` collects the stream after every layer.
+    ``rounded_stream``: every branch reads the stream rounded to bfloat16 (what serving in
+    bfloat16 does to a product's input at the least); the difference to the exact run says how
+    far rounding alone moves a row."""
     eps = cfg["norm"]["eps"]
     positions = torch.arange(len(tokens))
-    x = embed(W, cfg, tokens)
+    exact = embed(W, cfg, tokens)
     for i, layer in enumerate(cfg["layers"]):
+        x = exact.to(torch.bfloat16).to(F64) if rounded_stream else exact
         j = layer["weights_of"] if layer.get("weights_of") is not None else i
         p = f"l{j}."
         mx = layer["mixer"]
@@ -295,12 +299,13 @@ def forward(tokens: List[int], W: Dict[str, torch.Tensor], cfg: dict,
             right = matrix_memory_mixer(W, p + "mix.right.", mx["right"], x, eps) if gated \
                 else linear_recurrence_mixer(W, p + "mix.right.", mx["right"], x)
             y = mx["left_scale"] * left + mx["right_scale"] * right
-        x = x + offset_norm(y, W[p + "norm1"], eps)
+        exact = exact + offset_norm(y, W[p + "norm1"], eps)
         if layer.get("mlp"):
-            x = x + offset_norm(clamped_gated_unit(W, p + "mlp.", layer["mlp"], x), W[p + "norm2"], eps)
+            x = exact.to(torch.bfloat16).to(F64) if rounded_stream else exact
+            exact = exact + offset_norm(clamped_gated_unit(W, p + "mlp.", layer["mlp"], x), W[p + "norm2"], eps)
         if taps is not None:
-            taps.append(x.clone())
-    return offset_norm(x, W["final.norm"], eps) @ W["embed"].T
+            taps.append(exact.clone())
+    return offset_norm(exact, W["final.norm"], eps) @ W["embed"].T
 
 
 def greedy(prompt: List[int], n_new: int, W: Dict[str, torch.Tensor], cfg: dict) -> List[int]:

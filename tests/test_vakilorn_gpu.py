@@ -482,9 +482,13 @@ CASES = [(name, dtype) for name in SHAPES for dtype in ("float32", "bfloat16")]
 # mantissa before every product, and every branch's result is brought to unit size before it
 # joins the stream, so a branch's rounding reaches the stream undamped: about one percent a
 # row at these widths, with a tail of a few percent among hundreds of rows.  The largest row
-# and the middle one are both bounded.
+# and the middle one are both bounded.  A head whose result is what large terms leave of one
+# another before its unit norm moves far under any rounding of its inputs: the plain
+# implementation measures that itself, by rounding the stream each branch reads to bfloat16,
+# and a row may differ by 3 times what that rounding alone does to it; such rows stay few.
 TOL = {"float32": 2e-4, "bfloat16": 6e-2}
 TOL_MEDIAN = {"float32": 5e-5, "bfloat16": 2e-2}
+ROUNDING_FACTOR = 3.0
 
 
 @pytest.fixture(scope="module")
@@ -501,9 +505,21 @@ def folders(tmp_path_factory):
     return out
 
 
+class Oracle(dict):
+    """request -> logits [T, vocab]; ``moved[request][t]``: how far rounding the stream to
+    bfloat16 moves row t of the plain implementation itself (bfloat16 folders only)."""
+
+
 def _oracle(folder, prompts):
     cfg, tensors = P.read_folder(folder)
-    return {rid: P.forward(list(ids), tensors, cfg).to(torch.float32) for rid, ids in prompts.items()}
+    out = Oracle()
+    out.moved = {}
+    for rid, ids in prompts.items():
+        out[rid] = P.forward(list(ids), tensors, cfg).to(torch.float32)
+        if "bfloat16" in folder:
+            rounded = P.forward(list(ids), tensors, cfg, rounded_stream=True)
+            out.moved[rid] = [row_error(rounded[t], out[rid][t]) for t in range(len(ids))]
+    return out
 
 
 def row_error(row, ref) -> float:
@@ -516,16 +532,21 @@ def row_error(row, ref) -> float:
 
 def compare(rows, oracle, tol):
     assert rows
-    errs = []
+    errs, excused = [], 0
     for (rid, pos), row in sorted(rows.items()):
         err = row_error(row, oracle[rid][pos])
         assert err == err, f"NaN at request {rid} position {pos}"
+        moved = getattr(oracle, "moved", {}).get(rid)
+        if err > tol and moved is not None and err <= ROUNDING_FACTOR * moved[pos]:
+            excused += 1
+            continue
         assert err <= tol, (f"request {rid} position {pos} (page offset {pos % 64}): relative "
                             f"difference {err:.3e} > {tol:.1e}")
         errs.append(err)
     errs.sort()
     middle = errs[len(errs) // 2]
-    print(f"rows {len(errs)}: median {middle:.2e}, largest {errs[-1]:.2e}")
+    print(f"rows {len(errs)}: median {middle:.2e}, largest {errs[-1]:.2e}, excused {excused}")
+    assert excused <= max(1, len(rows) // 50), "too many ill-conditioned rows for the test to mean much"
     bound = TOL_MEDIAN["float32" if tol == TOL["float32"] else "bfloat16"]
     assert len(errs) < 8 or middle <= bound, f"the middle row differs by {middle:.3e} > {bound:.1e}"
     return errs[-1]
