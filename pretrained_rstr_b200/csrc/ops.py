@@ -203,6 +203,16 @@ def _declare(h: ctypes.CDLL) -> None:
     h.prb_mmem_supports.argtypes = [I, I]
     h.prb_mmem_step.argtypes = [P, L, P, L, I, I, I, I, I, I, P, P, P, P, P, P, P, P, P, I, I, I,
                                 I, I, I, F, F, F, F, I, P]
+    h.prb_lru_segment.argtypes = []
+    h.prb_lru_max_segments.argtypes = [I, I]
+    h.prb_lru_scan_segments.argtypes = [P, L, P, P, P, P, I, P, L, I, I, P, P, P, P, P, P, P, I, I,
+                                        I, I, I, F, I, P]
+    h.prb_lru_step_supports.argtypes = [I]
+    h.prb_lru_step.argtypes = [P, L, P, L, I, I, P, P, P, P, P, P, P, P, P, P, P, P, P, P, I, I, I,
+                               I, I, I, F, I, I, P]
+    for name in ("prb_lru_segment", "prb_lru_max_segments", "prb_lru_scan_segments",
+                 "prb_lru_step_supports", "prb_lru_step"):
+        getattr(h, name).restype = c_int
     h.prb_mmem_segment.argtypes = []
     h.prb_mmem_max_segments.argtypes = [I, I]
     h.prb_mmem_scan_supports.argtypes = [I]
@@ -1808,12 +1818,64 @@ def lru_gates(a_out, u, wa_t, wi_t, ba, bi, decay, blocks: int) -> None:
                                width, int(blocks), dtype_code(wa_t.dtype), _stream()), what)
 
 
+def lru_segment() -> int:
+    """Tokens of a segment of the gated linear recurrence's scan."""
+    return int(lib().prb_lru_segment())
+
+
+def lru_max_segments(t_cap: int, b_cap: int) -> int:
+    """Most segments a step of ``t_cap`` token rows and ``b_cap`` requests can have."""
+    return int(lib().prb_lru_max_segments(int(t_cap), int(b_cap)))
+
+
+def lru_step_supports(bw: int) -> bool:
+    """Whether the one-launch form takes blocks of ``bw`` channels."""
+    return bool(lib().prb_lru_step_supports(int(bw)))
+
+
+def lru_step(out, proj, y_col: int, x_col: int, y_bias, x_bias, conv_w, conv_b, wa_t, wi_t, ba, bi,
+             decay, state, conv_state, q_start, state_slot, positions, n_requests: int,
+             blocks: int, out_scale: float = 1.0) -> None:
+    """:func:`lru_conv`, :func:`lru_gates` and :func:`lru_scan` of a step of few tokens in one
+    launch: a CTA per (request, block of channels)."""
+    what = "lru_step"
+    n = proj.shape[0]
+    width, taps = conv_w.shape
+    if proj.dtype != torch.float32 or proj.stride(1) != 1 or max(y_col, x_col) + width > proj.shape[1] \
+            or out.stride(1) != 1 or out.shape[0] < n or out.shape[1] < width:
+        raise KernelArgumentError(f"{what}: proj must be float32 [T, ld] and out [T, >= width]")
+    bw = width // max(1, blocks)
+    _need(wa_t, None, "wa_t", what)
+    _need(wi_t, wa_t.dtype, "wi_t", what)
+    if width % blocks or tuple(wa_t.shape) != (blocks, bw, bw) or tuple(wi_t.shape) != (blocks, bw, bw):
+        raise KernelArgumentError(f"{what}: the block matrices must be [blocks, in, out]")
+    for name, t, size in (("y_bias", y_bias, width), ("x_bias", x_bias, width), ("conv_w", conv_w, width * taps),
+                          ("conv_b", conv_b, width), ("ba", ba, width), ("bi", bi, width), ("decay", decay, width)):
+        if t is not None:
+            _need(t, torch.float32, name, what)
+            if t.numel() != size:
+                raise KernelArgumentError(f"{what}: {name} must hold {size} numbers")
+    _need(state, torch.float32, "state", what)
+    _need(conv_state, torch.float32, "conv_state", what)
+    if state.shape[1] != width or tuple(conv_state.shape[1:]) != (taps - 1, width) or \
+            q_start.numel() < n_requests + 1:
+        raise KernelArgumentError(f"{what}: the state tensors do not fit")
+    _check(lib().prb_lru_step(_p(out), out.stride(0), _p(proj), proj.stride(0), int(y_col), int(x_col),
+                              _p(y_bias), _p(x_bias), _p(conv_w), _p(conv_b), _p(wa_t), _p(wi_t),
+                              _p(ba), _p(bi), _p(decay), _p(state), _p(conv_state), _p(q_start),
+                              _p(state_slot), _p(positions), n, int(n_requests), state.shape[0],
+                              width, int(blocks), taps, float(out_scale), dtype_code(wa_t.dtype),
+                              dtype_code(out.dtype), _stream()), what)
+
+
 def lru_scan(out, a_in, inp, proj, y_col: int, x_col: int, y_bias, x_bias, state, conv_state,
-             q_start, state_slot, positions, n_requests: int, out_scale: float = 1.0) -> None:
+             q_start, state_slot, positions, n_requests: int, out_scale: float = 1.0,
+             segments=None) -> None:
     """S_t = a_t S_(t-1) + inp_t per (request, channel) from and to ``state`` [slots, width]
     (zero at position 0); out[t, c] = S_t * gelu_tanh(proj[t, y_col + c] + y_bias[c]) *
     out_scale; ``conv_state`` then holds the request's last taps - 1 inputs proj[:, x_col + c] +
-    x_bias[c]."""
+    x_bias[c].  ``segments`` = (own, keep), two float32 workspaces [n, width] for n >=
+    lru_max_segments: portions run in segments of 64 tokens side by side (two launches)."""
     what = "lru_scan"
     _need(a_in, torch.float32, "a_in", what)
     _need(inp, torch.float32, "inp", what)
@@ -1826,6 +1888,21 @@ def lru_scan(out, a_in, inp, proj, y_col: int, x_col: int, y_bias, x_bias, state
             proj.dtype != torch.float32 or proj.stride(1) != 1 or \
             max(y_col, x_col) + width > proj.shape[1] or q_start.numel() < n_requests + 1:
         raise KernelArgumentError(f"{what}: shapes do not fit")
+    if segments is not None:
+        own, keep = segments
+        _need(own, torch.float32, "segments' own sums", what)
+        _need(keep, torch.float32, "segments' products", what)
+        if own.shape != keep.shape or own.shape[1] != width:
+            raise KernelArgumentError(f"{what}: the segment workspaces must be [n, width]")
+        code = lib().prb_lru_scan_segments(
+            _p(out), out.stride(0), _p(a_in), _p(inp), _p(own), _p(keep), own.shape[0], _p(proj),
+            proj.stride(0), int(y_col), int(x_col), _p(y_bias), _p(x_bias), _p(state),
+            _p(conv_state), _p(q_start), _p(state_slot), _p(positions), n, int(n_requests),
+            state.shape[0], width, taps, float(out_scale), dtype_code(out.dtype), _stream())
+        _check(code, what)
+        if code == 0 and n > 0:
+            add_launches(1)
+        return
     _check(lib().prb_lru_scan(_p(out), out.stride(0), _p(a_in), _p(inp), _p(proj), proj.stride(0),
                               int(y_col), int(x_col), _p(y_bias), _p(x_bias), _p(state),
                               _p(conv_state), _p(q_start), _p(state_slot), _p(positions), n,

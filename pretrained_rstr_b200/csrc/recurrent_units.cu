@@ -95,6 +95,7 @@ lru_gates_kernel(float* __restrict__ a_out, float* __restrict__ u, const W* __re
         float ra[LRU_TOK], ri[LRU_TOK];
 #pragma unroll
         for (int k = 0; k < LRU_TOK; ++k) ra[k] = ri[k] = 0.0f;
+#pragma unroll 4
         for (int i = 0; i < bw; ++i) {
             const float va = prb_to_float<W>(wa[(size_t)i * bw + o]);
             const float vi = prb_to_float<W>(wi[(size_t)i * bw + o]);
@@ -166,6 +167,217 @@ lru_scan_kernel(O* __restrict__ out, long out_ld, const float* __restrict__ a_in
         if (back <= n) v = proj[(size_t)(r1 - back) * ld + x_col + c] + xb;
         else {
             const int ko = k + n;                    // (k + n < keep here)
+            v = 0.0f;
+#pragma unroll
+            for (int z = 0; z < LRU_MAX_TAPS; ++z) if (z == ko) v = old[z];
+        }
+        cs[(size_t)k * width] = v;
+    }
+}
+
+// ------------------------------------------------- (1) steps of few tokens: one launch
+// A CTA per (request, block of channels), a thread per channel of the block: the convolution
+// of up to LRU_TOK tokens into shared memory, the block matrices for those tokens (weights
+// read once per group of tokens), then the recurrence over them in the thread's registers,
+// from and to the slot; the saved inputs are brought up to date at the end.  The sums are those
+// of the three kernels, in their order.
+struct LruStepArgs {
+    void* out; long out_ld;
+    const float* proj; long ld; int y_col, x_col;
+    const float* y_bias; const float* x_bias;
+    const float* conv_w; const float* conv_b;
+    const void* wa_t; const void* wi_t;
+    const float* ba; const float* bi; const float* decay;
+    float* state; float* conv_state;
+    const int* q_start; const int* state_slot; const int* positions;
+    int n_tokens, n_slots, width, bw, taps;
+    float out_scale;
+};
+
+template <typename W, typename O>
+__global__ void lru_step_kernel(LruStepArgs g) {
+    extern __shared__ float us[];                    // [LRU_TOK][bw]
+    prb_grid_launch_dependents();
+    const int b = blockIdx.x, blk = blockIdx.y;
+    const int r0 = g.q_start[b], r1 = min(g.q_start[b + 1], g.n_tokens);
+    if (r0 >= r1 || r0 < 0) return;
+    const int bw = g.bw, taps = g.taps, width = g.width;
+    const int slot = g.state_slot[b];
+    const bool has_slot = slot >= 0 && slot < g.n_slots;
+    const int p0 = g.positions[r0];
+    const int o = threadIdx.x;
+    const bool live = o < bw;
+    const int c = blk * bw + (live ? o : 0);
+    const W* wa = reinterpret_cast<const W*>(g.wa_t) + (size_t)blk * bw * bw;
+    const W* wi = reinterpret_cast<const W*>(g.wi_t) + (size_t)blk * bw * bw;
+    O* out = reinterpret_cast<O*>(g.out);
+    const float xb = g.x_bias ? g.x_bias[c] : 0.0f, yb = g.y_bias ? g.y_bias[c] : 0.0f;
+    const float cb = g.conv_b ? g.conv_b[c] : 0.0f;
+    const float dc = g.decay[c], bac = g.ba[c], bic = g.bi[c];
+    const float* cs_old = g.conv_state + (size_t)(has_slot ? slot : 0) * (taps - 1) * width + c;
+    float s = (live && p0 > 0 && has_slot) ? g.state[(size_t)slot * width + c] : 0.0f;
+    for (int tb = r0; tb < r1; tb += LRU_TOK) {
+        const int nt = min(LRU_TOK, r1 - tb);
+        __syncthreads();                             // the group before has been consumed
+        if (live) {
+            for (int k = 0; k < nt; ++k) {
+                const int t = tb + k, p = p0 + (t - r0);
+                float acc = cb;
+                for (int j = 0; j < taps; ++j) {
+                    const int d = taps - 1 - j, sp = p - d;
+                    if (sp < 0) continue;
+                    float xv = 0.0f;
+                    if (sp >= p0) xv = g.proj[(size_t)(t - d) * g.ld + g.x_col + c] + xb;
+                    else if (has_slot) xv = cs_old[(size_t)(taps - 1 - (p0 - sp)) * width];
+                    acc = fmaf(g.conv_w[(size_t)c * taps + j], xv, acc);
+                }
+                us[k * bw + o] = acc;
+            }
+            for (int k = nt; k < LRU_TOK; ++k) us[k * bw + o] = 0.0f;
+        }
+        __syncthreads();
+        if (!live) continue;
+        float ra[LRU_TOK], ri[LRU_TOK];
+#pragma unroll
+        for (int k = 0; k < LRU_TOK; ++k) ra[k] = ri[k] = 0.0f;
+#pragma unroll 4
+        for (int i = 0; i < bw; ++i) {
+            const float va = prb_to_float<W>(wa[(size_t)i * bw + o]);
+            const float vi = prb_to_float<W>(wi[(size_t)i * bw + o]);
+#pragma unroll
+            for (int k = 0; k < LRU_TOK; ++k) {
+                const float uu = us[k * bw + i];
+                ra[k] = fmaf(va, uu, ra[k]);
+                ri[k] = fmaf(vi, uu, ri[k]);
+            }
+        }
+#pragma unroll
+        for (int k = 0; k < LRU_TOK; ++k) {
+            if (k >= nt) break;
+            const float r = ru_sigmoid(ra[k] + bac), gi = ru_sigmoid(ri[k] + bic);
+            const float la = dc * r;
+            const float in = sqrtf(fmaxf(-expm1f(2.0f * la), 0.0f)) * gi * us[k * bw + o];
+            s = fmaf(expf(la), s, in);
+            const float y = prb_activate(g.proj[(size_t)(tb + k) * g.ld + g.y_col + c] + yb, PRB_ACT_GELU_TANH);
+            out[(size_t)(tb + k) * g.out_ld + c] = prb_from_float<O>(s * y * g.out_scale);
+        }
+    }
+    // (the convolution read the saved inputs above; every thread of the CTA is past its last
+    // read of its own channel's rows, which no other thread touches)
+    if (!live || !has_slot) return;
+    g.state[(size_t)slot * width + c] = s;
+    const int keep = taps - 1, n = r1 - r0;
+    float* cs = g.conv_state + (size_t)slot * keep * width + c;
+    float old[LRU_MAX_TAPS];
+#pragma unroll
+    for (int k = 0; k < LRU_MAX_TAPS; ++k) old[k] = (k < keep && p0 > 0) ? cs[(size_t)k * width] : 0.0f;
+#pragma unroll
+    for (int k = 0; k < LRU_MAX_TAPS; ++k) {
+        if (k >= keep) break;
+        const int back = keep - k;
+        float v;
+        if (back <= n) v = g.proj[(size_t)(r1 - back) * g.ld + g.x_col + c] + xb;
+        else {
+            const int ko = k + n;
+            v = 0.0f;
+#pragma unroll
+            for (int z = 0; z < LRU_MAX_TAPS; ++z) if (z == ko) v = old[z];
+        }
+        cs[(size_t)k * width] = v;
+    }
+}
+
+// ------------------------------------------------- (1) long portions: the scan in segments
+// Segment z of the launch is segment s of request b (numbered in request order).  Pass 1: a
+// thread per (segment, channel) builds, from zero, what the segment's own tokens leave and the
+// product of its decays.  Pass 2: a thread per (segment, channel) first walks the request's
+// earlier segments, U <- product U + own from the carried state, then runs its own tokens with
+// outputs; a request's last segment leaves the state and the saved inputs in the slot.
+constexpr int LRU_SEG = 64;
+__device__ __forceinline__ bool lru_find_segment(const int* q_start, int n_requests, int z, int& b,
+                                                 int& s, int& nseg, int& base) {
+    base = 0;
+    for (b = 0; b < n_requests; ++b) {
+        const int n = q_start[b + 1] - q_start[b];
+        nseg = n > 0 ? (n + LRU_SEG - 1) / LRU_SEG : 0;
+        if (z < base + nseg) {
+            s = z - base;
+            return true;
+        }
+        base += nseg;
+    }
+    return false;
+}
+
+__global__ void __launch_bounds__(128)
+lru_seg_own_kernel(float* __restrict__ seg_own, float* __restrict__ seg_keep,
+                   const float* __restrict__ a_in, const float* __restrict__ in,
+                   const int* __restrict__ q_start, int n_tokens, int n_requests, int width) {
+    prb_grid_launch_dependents();
+    int b, s, nseg, base;
+    if (!lru_find_segment(q_start, n_requests, blockIdx.x, b, s, nseg, base)) return;
+    const int c = blockIdx.y * blockDim.x + threadIdx.x;
+    if (c >= width || s == nseg - 1) return;         // (a last segment's own sum is never needed)
+    const int t0 = q_start[b] + s * LRU_SEG, t1 = min(min(q_start[b + 1], n_tokens), t0 + LRU_SEG);
+    float own = 0.0f, keep = 1.0f;
+#pragma unroll 8
+    for (int r = t0; r < t1; ++r) {
+        const float a = a_in[(size_t)r * width + c];
+        own = fmaf(a, own, in[(size_t)r * width + c]);
+        keep *= a;
+    }
+    seg_own[(size_t)blockIdx.x * width + c] = own;
+    seg_keep[(size_t)blockIdx.x * width + c] = keep;
+}
+
+template <typename O>
+__global__ void __launch_bounds__(128)
+lru_seg_scan_kernel(O* __restrict__ out, long out_ld, const float* __restrict__ a_in,
+                    const float* __restrict__ in, const float* __restrict__ seg_own,
+                    const float* __restrict__ seg_keep, const float* __restrict__ proj, long ld,
+                    int y_col, int x_col, const float* __restrict__ y_bias,
+                    const float* __restrict__ x_bias, float* __restrict__ state,
+                    float* __restrict__ conv_state, const int* __restrict__ q_start,
+                    const int* __restrict__ state_slot, const int* __restrict__ positions,
+                    int n_tokens, int n_requests, int n_slots, int width, int taps,
+                    float out_scale) {
+    prb_grid_launch_dependents();
+    int b, sg, nseg, base;
+    if (!lru_find_segment(q_start, n_requests, blockIdx.x, b, sg, nseg, base)) return;
+    const int c = blockIdx.y * blockDim.x + threadIdx.x;
+    if (c >= width) return;
+    const int r0 = q_start[b], r1 = min(q_start[b + 1], n_tokens);
+    const int slot = state_slot[b];
+    const bool has_slot = slot >= 0 && slot < n_slots;
+    const int p0 = positions[r0];
+    float s = (p0 > 0 && has_slot) ? state[(size_t)slot * width + c] : 0.0f;
+    for (int z = 0; z < sg; ++z)
+        s = fmaf(seg_keep[(size_t)(base + z) * width + c], s, seg_own[(size_t)(base + z) * width + c]);
+    const int t0 = r0 + sg * LRU_SEG, t1 = min(r1, t0 + LRU_SEG);
+    const float yb = y_bias ? y_bias[c] : 0.0f;
+#pragma unroll 8
+    for (int r = t0; r < t1; ++r) {
+        s = fmaf(a_in[(size_t)r * width + c], s, in[(size_t)r * width + c]);
+        const float y = prb_activate(proj[(size_t)r * ld + y_col + c] + yb, PRB_ACT_GELU_TANH);
+        out[(size_t)r * out_ld + c] = prb_from_float<O>(s * y * out_scale);
+    }
+    if (!has_slot || sg != nseg - 1) return;
+    state[(size_t)slot * width + c] = s;
+    const int keep = taps - 1;
+    const int n = r1 - r0;
+    const float xb = x_bias ? x_bias[c] : 0.0f;
+    float* cs = conv_state + (size_t)slot * keep * width + c;
+    float old[LRU_MAX_TAPS];
+#pragma unroll
+    for (int k = 0; k < LRU_MAX_TAPS; ++k) old[k] = (k < keep && p0 > 0) ? cs[(size_t)k * width] : 0.0f;
+#pragma unroll
+    for (int k = 0; k < LRU_MAX_TAPS; ++k) {
+        if (k >= keep) break;
+        const int back = keep - k;
+        float v;
+        if (back <= n) v = proj[(size_t)(r1 - back) * ld + x_col + c] + xb;
+        else {
+            const int ko = k + n;
             v = 0.0f;
 #pragma unroll
             for (int z = 0; z < LRU_MAX_TAPS; ++z) if (z == ko) v = old[z];
@@ -672,6 +884,75 @@ PRB_API int prb_lru_scan(void* out, long out_ld, const float* a_in, const float*
         lru_scan_kernel<__nv_bfloat16><<<grid, 128, 0, stream>>>(
             (__nv_bfloat16*)out, out_ld, a_in, in, proj, ld, y_col, x_col, y_bias, x_bias, state,
             conv_state, q_start, state_slot, positions, n_tokens, n_slots, width, taps, out_scale);
+    else
+        return PRB_E_DTYPE;
+    PRB_LAUNCH_CHECK();
+    return 0;
+}
+
+// The scan in segments side by side (two launches): seg_own and seg_keep are [segments, width]
+// for segments >= prb_lru_max_segments(n_tokens, n_requests).
+PRB_API int prb_lru_segment() { return LRU_SEG; }
+PRB_API int prb_lru_max_segments(int t_cap, int b_cap) { return t_cap / LRU_SEG + b_cap; }
+PRB_API int prb_lru_scan_segments(void* out, long out_ld, const float* a_in, const float* in,
+                                  float* seg_own, float* seg_keep, int segments,
+                                  const float* proj, long ld, int y_col, int x_col,
+                                  const float* y_bias, const float* x_bias, float* state,
+                                  float* conv_state, const int* q_start, const int* state_slot,
+                                  const int* positions, int n_tokens, int n_requests, int n_slots,
+                                  int width, int taps, float out_scale, int out_dtype,
+                                  cudaStream_t stream) {
+    if (n_tokens <= 0 || n_requests <= 0) return 0;
+    if (width <= 0 || taps < 1 || taps > LRU_MAX_TAPS) return PRB_E_SIZE;
+    const int most = prb_lru_max_segments(n_tokens, n_requests);
+    if (segments < most || most > 65535 * 32) return PRB_E_SIZE;
+    if (out_dtype != PRB_F32 && out_dtype != PRB_BF16) return PRB_E_DTYPE;
+    dim3 grid(most, (width + 127) / 128);
+    lru_seg_own_kernel<<<grid, 128, 0, stream>>>(seg_own, seg_keep, a_in, in, q_start, n_tokens,
+                                                 n_requests, width);
+    PRB_LAUNCH_CHECK();
+    if (out_dtype == PRB_F32)
+        lru_seg_scan_kernel<float><<<grid, 128, 0, stream>>>(
+            (float*)out, out_ld, a_in, in, seg_own, seg_keep, proj, ld, y_col, x_col, y_bias,
+            x_bias, state, conv_state, q_start, state_slot, positions, n_tokens, n_requests,
+            n_slots, width, taps, out_scale);
+    else
+        lru_seg_scan_kernel<__nv_bfloat16><<<grid, 128, 0, stream>>>(
+            (__nv_bfloat16*)out, out_ld, a_in, in, seg_own, seg_keep, proj, ld, y_col, x_col,
+            y_bias, x_bias, state, conv_state, q_start, state_slot, positions, n_tokens,
+            n_requests, n_slots, width, taps, out_scale);
+    PRB_LAUNCH_CHECK();
+    return 0;
+}
+
+// 1 if the one-launch form takes blocks of `bw` channels (a thread per channel of a block).
+PRB_API int prb_lru_step_supports(int bw) { return bw > 0 && bw <= 1024 ? 1 : 0; }
+
+// Convolution, gates and recurrence of a step of few tokens in one launch (see
+// lru_step_kernel); wa_t, wi_t: [blocks, in, out].
+PRB_API int prb_lru_step(void* out, long out_ld, const float* proj, long ld, int y_col, int x_col,
+                         const float* y_bias, const float* x_bias, const float* conv_w,
+                         const float* conv_b, const void* wa_t, const void* wi_t, const float* ba,
+                         const float* bi, const float* decay, float* state, float* conv_state,
+                         const int* q_start, const int* state_slot, const int* positions,
+                         int n_tokens, int n_requests, int n_slots, int width, int blocks,
+                         int taps, float out_scale, int w_dtype, int out_dtype,
+                         cudaStream_t stream) {
+    if (n_tokens <= 0 || n_requests <= 0) return 0;
+    if (width <= 0 || blocks <= 0 || width % blocks != 0 || blocks > 65535 || taps < 1 ||
+        taps > LRU_MAX_TAPS || !prb_lru_step_supports(width / blocks))
+        return PRB_E_SIZE;
+    const int bw = width / blocks;
+    LruStepArgs g{out, out_ld, proj, ld, y_col, x_col, y_bias, x_bias, conv_w, conv_b, wa_t, wi_t,
+                  ba, bi, decay, state, conv_state, q_start, state_slot, positions, n_tokens,
+                  n_slots, width, bw, taps, out_scale};
+    const size_t smem = (size_t)LRU_TOK * bw * sizeof(float);
+    const int threads = (bw + 31) / 32 * 32;
+    dim3 grid(n_requests, blocks);
+    if (w_dtype == PRB_F32 && out_dtype == PRB_F32)
+        lru_step_kernel<float, float><<<grid, threads, smem, stream>>>(g);
+    else if (w_dtype == PRB_BF16 && out_dtype == PRB_BF16)
+        lru_step_kernel<__nv_bfloat16, __nv_bfloat16><<<grid, threads, smem, stream>>>(g);
     else
         return PRB_E_DTYPE;
     PRB_LAUNCH_CHECK();

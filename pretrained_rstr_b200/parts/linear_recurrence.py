@@ -14,7 +14,9 @@ and per channel, with ``decay_constant`` c (8 in Griffin) and a learned lambda,
 
 The result is Wo (S * y).  The state S and the convolution's last ``taps - 1`` inputs are
 per-request STATE of the cache manager (a slot per live request, zero at position 0), so a
-prompt may be cut anywhere and decoding is the same kernels with one token.  Wy and Wx are
+prompt may be cut anywhere and decoding is the same kernels with one token.  Steps of few
+tokens are one launch (a CTA per (request, block)); longer portions run the convolution, the
+gates and then the recurrence in segments of 64 tokens side by side.  Wy and Wx are
 one product whose 32-bit result feeds everything after it unrounded; the block matrices, the
 gates, the decays, the recurrence and the state are 32-bit.  Sizes, taps, blocks, the decay's
 constant and the constant on the result are parameters.
@@ -71,6 +73,7 @@ class GatedLinearRecurrence(Mixer):
         lam = f32(need("lambda", (self.inner,)))
         self.decay = (-float(p.get("decay_constant", 8.0)) * torch.nn.functional.softplus(lam)).contiguous()
         self.out = padded_linear(need("out", (self.width, self.inner)), runtime)
+        self.one_launch = torch.cuda.is_available() and ops.lru_step_supports(bw)
 
     def state_specs(self):
         return [StateSpec("lru_state", (self.inner,), torch.float32),
@@ -92,15 +95,30 @@ class GatedLinearRecurrence(Mixer):
         state, inputs = cache.state["lru_state"], cache.state["lru_inputs"]
         proj = self._proj = self.input.run(ctx, h)
         cols = self.input.cols
+        gated = ctx.scratch_zero("lru_gated", (cap, self.out.n_in), self.runtime.dtype)[:t]
+        requests = ctx.layout.b_cap
+        if ctx.layout.t_cap <= ops.lru_segment() and self.one_launch:
+            # a step of few tokens: convolution, gates and recurrence in one launch
+            ops.lru_step(gated, proj, cols["y"][0], cols["x"][0], self.y_bias, self.x_bias,
+                         self.conv_w, self.conv_b, self.wa_t, self.wi_t, self.ba, self.bi,
+                         self.decay, state, inputs, ctx.q_start, ctx.state_slot, ctx.positions,
+                         requests, self.blocks, out_scale=self.out_scale)
+            self.out.forward(ctx, gated, x, resid=x if accumulate else None)
+            return
         u = ctx.scratch("lru_u", (cap, self.inner), torch.float32)[:t]
         a = ctx.scratch("lru_a", (cap, self.inner), torch.float32)[:t]
         ops.lru_conv(u, proj, cols["x"][0], self.x_bias, self.conv_w, self.conv_b, inputs,
                      ctx.seq_of_token, ctx.positions, ctx.q_start, ctx.state_slot)
         ops.lru_gates(a, u, self.wa_t, self.wi_t, self.ba, self.bi, self.decay, self.blocks)
-        gated = ctx.scratch_zero("lru_gated", (cap, self.out.n_in), self.runtime.dtype)[:t]
+        # portions are cut into segments that run side by side (workspaces sized once, for the
+        # largest step the runtime takes)
+        n = ops.lru_max_segments(max(ctx.runtime.max_batched_tokens, ctx.layout.t_cap),
+                                 max(ctx.runtime.max_requests, requests))
+        segments = (ctx.scratch("lru_seg_own", (n, self.inner), torch.float32),
+                    ctx.scratch("lru_seg_keep", (n, self.inner), torch.float32))
         ops.lru_scan(gated, a, u, proj, cols["y"][0], cols["x"][0], self.y_bias, self.x_bias,
-                     state, inputs, ctx.q_start, ctx.state_slot, ctx.positions, ctx.layout.b_cap,
-                     out_scale=self.out_scale)
+                     state, inputs, ctx.q_start, ctx.state_slot, ctx.positions, requests,
+                     out_scale=self.out_scale, segments=segments)
         self.out.forward(ctx, gated, x, resid=x if accumulate else None)
 
 

@@ -61,8 +61,10 @@ class RecurrenceCase:
         i = torch.sigmoid(torch.einsum("boi,tbi->tbo", self.ri.double(), ub) + self.ri_b.double()).reshape(T, -1)
         return P.gated_recurrence_states(u, r, i, self.lam.double()) * P.tanh_gelu(y.double() + self.y_b.double())
 
-    def run(self, parts, scale=1.0):
-        """parts: (slot, first position, y, x) per request of one step."""
+    def run(self, parts, scale=1.0, mode="scan"):
+        """parts: (slot, first position, y, x) per request of one step; ``mode``: "scan" (three
+        kernels, a thread per (request, channel)), "segments" (the scan in segments side by
+        side) or "step" (one launch)."""
         from pretrained_rstr_b200.csrc import ops
         pad = lambda n: torch.zeros(n, 8)
         proj = torch.cat([torch.cat([pad(y.shape[0]), y, pad(y.shape[0]), x], dim=1)
@@ -75,30 +77,41 @@ class RecurrenceCase:
         out = torch.zeros(t, self.inner + 8, device=DEV)
         dev = lambda v: v.to(DEV).contiguous()
         decay = dev(-8.0 * torch.nn.functional.softplus(self.lam))
+        if mode == "step":
+            ops.lru_step(out, proj, y_col, x_col, dev(self.y_b), dev(self.x_b), dev(self.conv),
+                         dev(self.conv_b), dev(self.ra.transpose(1, 2)), dev(self.ri.transpose(1, 2)),
+                         dev(self.ra_b.reshape(-1)), dev(self.ri_b.reshape(-1)), decay, self.state,
+                         self.inputs, qs, slots, pos, len(parts) + 1, self.blocks, out_scale=scale)
+            return out.cpu().double()[:, :self.inner]
+        segments = None
+        if mode == "segments":
+            n = ops.lru_max_segments(t, len(parts) + 1) + 1
+            segments = (torch.full((n, self.inner), 3.0, device=DEV), torch.full((n, self.inner), 3.0, device=DEV))
         ops.lru_conv(u, proj, x_col, dev(self.x_b), dev(self.conv), dev(self.conv_b), self.inputs,
                      seq, pos, qs, slots)
         ops.lru_gates(a, u, dev(self.ra.transpose(1, 2)), dev(self.ri.transpose(1, 2)),
                       dev(self.ra_b.reshape(-1)), dev(self.ri_b.reshape(-1)), decay, self.blocks)
         ops.lru_scan(out, a, u, proj, y_col, x_col, dev(self.y_b), dev(self.x_b), self.state,
-                     self.inputs, qs, slots, pos, len(parts) + 1, out_scale=scale)
+                     self.inputs, qs, slots, pos, len(parts) + 1, out_scale=scale, segments=segments)
         return out.cpu().double()[:, :self.inner]
 
 
+@pytest.mark.parametrize("mode", ["scan", "segments", "step"])
 @pytest.mark.parametrize("inner,blocks,taps", [(48, 3, 3), (40, 1, 4), (64, 8, 1), (130, 2, 2),
                                                (36, 36, 6), (256, 4, 4)])
-def test_linear_recurrence_kernels(inner, blocks, taps):
+def test_linear_recurrence_kernels(inner, blocks, taps, mode):
     """A whole sequence at once; the same in portions down to one token (the convolution's taps
     cross every cut) beside another request; a slot's earlier state and saved inputs are not
     read at position 0 and are carried from then on."""
     case = RecurrenceCase(inner, blocks, taps, seed=inner + taps)
-    n = 83
+    n = 183
     y, x = case.rows(n)
     y2, x2 = case.rows(29)
     want, want2 = case.plain(y, x), case.plain(y2, x2)
-    got = case.run([(1, 0, y, x)])
+    got = case.run([(1, 0, y, x)], mode=mode)
     assert torch.allclose(got, want, atol=2e-5, rtol=1e-5)
     at, k = 0, 0
-    cuts = [1, 2, 1, 5, 1, 1, 17, 2, 30, 3]
+    cuts = [1, 2, 1, 5, 1, 1, 17, 2, 70, 3, 64]
     other = 0
     pieces = []
     while at < n:
@@ -108,7 +121,7 @@ def test_linear_recurrence_kernels(inner, blocks, taps):
         if other < 29:                                     # another request rides along
             mo = min(4, 29 - other)
             parts.insert(0, (0, other, y2[other:other + mo], x2[other:other + mo]))
-        got = case.run(parts, scale=0.5)
+        got = case.run(parts, scale=0.5, mode=mode)
         if len(parts) == 2:
             assert torch.allclose(got[:mo] * 2, want2[other:other + mo], atol=2e-5, rtol=1e-5)
             other += mo
@@ -128,9 +141,9 @@ def test_linear_recurrence_far_token_stands_out():
     x[3] *= 40.0
     want = case.plain(y, x)
     assert float(want[n - 1].abs().max()) > 1.0            # the far token still matters
-    got = [case.run([(1, 0, y[:5], x[:5])])]
+    got = [case.run([(1, 0, y[:5], x[:5])], mode="step")]
     for t in range(5, n):
-        got.append(case.run([(1, t, y[t:t + 1], x[t:t + 1])]))
+        got.append(case.run([(1, t, y[t:t + 1], x[t:t + 1])], mode="step" if t % 2 else "scan"))
     assert torch.allclose(torch.cat(got), want, atol=1e-4, rtol=1e-4)
 
 
