@@ -132,10 +132,10 @@ class VakilornConfig(ModelConfig):
             where = f"layers[{i}]"
             if not isinstance(entry, dict) or entry.get("type") not in _TYPES:
                 raise ConfigError(f"config.json: {where}.type must be one of {list(_TYPES)}")
-            mx = entry.get("mixer")
-            if not isinstance(mx, dict):
-                raise ConfigError(f"config.json: {where}.mixer must be an object")
             src = entry.get("weights_of")
+            mx = entry.get("mixer")
+            if not isinstance(mx, dict) and src is None:
+                raise ConfigError(f"config.json: {where}.mixer must be an object")
             if src is not None:
                 if isinstance(src, bool) or not isinstance(src, int) or not 0 <= src < len(self.layers) \
                         or src == i:
@@ -145,9 +145,10 @@ class VakilornConfig(ModelConfig):
                 if other.get("weights_of") is not None:
                     raise ConfigError(f"config.json: {where}.weights_of names layer {src}, which has "
                                       f"no tensors of its own")
-                if any(other.get(k) != entry.get(k) for k in ("type", "mixer", "mlp")):
+                if not isinstance(other, dict) or other.get("type") != entry.get("type"):
                     raise ConfigError(f"config.json: {where} uses layer {src}'s tensors but "
                                       f"describes another layer")
+                continue            # (it runs layer src's parts, which are checked there)
             if entry["type"] in ("parallel", "parallel_2"):
                 _check_left(mx.get("left"), where + ".mixer.left")
                 right = mx.get("right")
@@ -282,6 +283,12 @@ class VakilornConfig(ModelConfig):
         place = {i: k for k, i in enumerate(self.own_layers())}
         return [RunEntry(place[i if e.get("weights_of") is None else e["weights_of"]], i)
                 for i, e in enumerate(self.layers)]
+
+    def layer_entry(self, i: int) -> Dict[str, Any]:
+        """The entry whose sizes layer i runs with: its own, or, for a layer that runs another
+        layer's tensors, that layer's (the tensors' shapes are that layer's)."""
+        src = self.layers[i].get("weights_of")
+        return self.layers[i if src is None else src]
 
     def embedding_spec(self) -> PartSpec:
         bg = self.embedding.get("bigram")

@@ -42,9 +42,14 @@ class MatrixMemory(Mixer):
         self.q_scale = float(p.get("q_scale", self.dim ** -0.5))
         self.out_scale = float(p.get("out_scale", 1.0))
         self.runtime = runtime
-        if torch.cuda.is_available() and not ops.mmem_supports(self.dim, self.vdim):
-            raise ValueError(f"matrix_memory: a head of {self.dim} x {self.vdim} does not fit a "
-                             f"CTA's shared memory")
+        gpu = torch.cuda.is_available()
+        # the one-launch kernel keeps a head's state in shared memory; the scan keeps a column
+        # over up to 32 lanes of 16 numbers: either takes every step where the other cannot
+        self.step_ok = gpu and ops.mmem_supports(self.dim, self.vdim)
+        self.scan_ok = gpu and ops.mmem_scan_supports(self.dim)
+        if gpu and not (self.step_ok or self.scan_ok):
+            raise ValueError(f"matrix_memory: heads of {self.dim} x {self.vdim} are beyond both "
+                             f"kernels (512 numbers a key, or a state of 200 KB)")
 
         def need(name, shape):
             t = store.get(w[name])
@@ -62,7 +67,6 @@ class MatrixMemory(Mixer):
         self.f_bias = f32(need("f_bias", (self.heads,))) if w.get("f_bias") else None
         self.norm = f32(need("norm", (hv,)))
         self.out = padded_linear(need("out", (self.width, hv)), runtime)
-        self.scan_ok = torch.cuda.is_available() and ops.mmem_scan_supports(self.dim)
         self.sm_count = ops.sm_count() if torch.cuda.is_available() else 148
 
     def state_specs(self):
@@ -89,7 +93,8 @@ class MatrixMemory(Mixer):
         columns = (c["q"][0], c["k"][0], c["v"][0], c["i"][0], c["f"][0], c["gate"][0])
         states = (cache.state["mmem_s"], cache.state["mmem_n"], cache.state["mmem_m"])
         requests = ctx.layout.b_cap
-        if ctx.layout.t_cap <= ops.mmem_segment() or not self.scan_ok:
+        few = ctx.layout.t_cap <= ops.mmem_segment()
+        if (few and self.step_ok) or not self.scan_ok:
             # a step of few tokens: one launch, a CTA per (head, request)
             ops.mmem_step(gated, proj, columns, self.i_bias, self.f_bias, self.norm, *states,
                           ctx.q_start, ctx.state_slot, ctx.positions, requests, self.heads,
@@ -101,11 +106,12 @@ class MatrixMemory(Mixer):
             n = ops.mmem_max_segments(max(ctx.runtime.max_batched_tokens, ctx.layout.t_cap),
                                       max(ctx.runtime.max_requests, requests))
             big, small = (n, self.heads, self.vdim, self.dim), (n, self.heads, self.dim)
-            segments = (ctx.scratch("mmem_seg_own", big, torch.float32),
-                        ctx.scratch("mmem_seg_start", big, torch.float32),
-                        ctx.scratch("mmem_seg_own_n", small, torch.float32),
-                        ctx.scratch("mmem_seg_start_n", small, torch.float32),
-                        ctx.scratch("mmem_seg_keep", (n, self.heads), torch.float32))
+            segments = None if few else (
+                ctx.scratch("mmem_seg_own", big, torch.float32),
+                ctx.scratch("mmem_seg_start", big, torch.float32),
+                ctx.scratch("mmem_seg_own_n", small, torch.float32),
+                ctx.scratch("mmem_seg_start_n", small, torch.float32),
+                ctx.scratch("mmem_seg_keep", (n, self.heads), torch.float32))
             raw = ctx.scratch("mmem_raw", (cap, self.heads * self.vdim), torch.float32)[:t]
             gates = ctx.scratch("mmem_gates", (cap, self.heads, 4), torch.float32)[:t]
             cols = self.vdim           # value columns a CTA: halved while the GPU is not filled twice

@@ -71,7 +71,7 @@ def test_registry_and_structure():
 @pytest.mark.parametrize("change,where", [
     (lambda r: r["layers"][0].__setitem__("type", "attention"), "type"),
     (lambda r: r["layers"][0].__setitem__("weights_of", 0), "weights_of"),
-    (lambda r: r["layers"][0]["mlp"].__setitem__("ff", 21), "another layer"),
+    (lambda r: r["layers"][0].__setitem__("type", "parallel_2"), "another layer"),
     (lambda r: [r["layers"][i]["mixer"]["right"].__setitem__("blocks", 5) for i in (0, 2)], "blocks"),
     (lambda r: r["layers"][1]["mixer"]["rot"].__setitem__("dims", 6), "dims"),
     (lambda r: r["layers"][3]["mixer"]["left"]["rot"]["scaling"].__setitem__("original", 8), "scaling"),
