@@ -56,6 +56,21 @@ __global__ void embed_pair_kernel(float* __restrict__ out, const int* __restrict
         o[i] = fmaf(prb_to_float<W>(e[i]), scale, prb_to_float<W>(p[i]));
 }
 
+// --------------------------------------------------------------- a gate per coordinate
+// out[t, i] = in[t, i] * sigmoid(gate[t, i]) for i < n (in, gate: 32-bit rows of pitch in_ld /
+// gate_ld; out in the activation type).
+template <typename O>
+__global__ void gate_mul_kernel(O* __restrict__ out, long out_ld, const float* __restrict__ in,
+                                long in_ld, const float* __restrict__ gate, long gate_ld, int n,
+                                long total) {
+    prb_grid_launch_dependents();
+    const long e = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (e >= total) return;
+    const long t = e / n;
+    const int i = (int)(e - t * n);
+    out[t * out_ld + i] = prb_from_float<O>(in[t * in_ld + i] * sigmoidf_(gate[t * gate_ld + i]));
+}
+
 // ------------------------------------------------------------------------- RMS norm
 struct RmsArgs {
     void* out;              // [n_rows, width] in O, or null
@@ -246,6 +261,23 @@ PRB_API int prb_embed_pair(float* out, const int* tokens, const int* positions, 
             out, tokens, positions, seq, q_start, state_slot, prev_state,
             (const __nv_bfloat16*)table, (const __nv_bfloat16*)pairs, n_tokens, width, vocab,
             buckets, mul_prev, mul_cur, n_slots, b_cap, scale, status);
+    else
+        return PRB_E_DTYPE;
+    PRB_LAUNCH_CHECK();
+    return 0;
+}
+
+PRB_API int prb_gate_mul(void* out, long out_ld, const float* in, long in_ld, const float* gate,
+                         long gate_ld, int n_rows, int n, int out_dtype, cudaStream_t stream) {
+    if (n_rows <= 0 || n <= 0) return 0;
+    const long total = (long)n_rows * n;
+    const unsigned blocks = (unsigned)((total + 255) / 256);
+    if (out_dtype == PRB_F32)
+        gate_mul_kernel<float><<<blocks, 256, 0, stream>>>((float*)out, out_ld, in, in_ld, gate,
+                                                           gate_ld, n, total);
+    else if (out_dtype == PRB_BF16)
+        gate_mul_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>((__nv_bfloat16*)out, out_ld, in,
+                                                                   in_ld, gate, gate_ld, n, total);
     else
         return PRB_E_DTYPE;
     PRB_LAUNCH_CHECK();

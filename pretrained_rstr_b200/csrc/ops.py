@@ -134,6 +134,8 @@ def _declare(h: ctypes.CDLL) -> None:
     h.prb_sample_workspace_words.restype = c_int
     h.prb_embed_pair.argtypes = [P, P, P, P, P, P, P, P, P, I, I, I, L, L, L, I, I, I, F, P, P]
     h.prb_rms_norm.argtypes = [P, P, P, P, P, L, P, P, P, P, I, I, I, F, F, I, I, P, P]
+    h.prb_gate_mul.argtypes = [P, L, P, L, P, L, I, I, I, P]
+    h.prb_gate_mul.restype = c_int
     h.prb_gated_pair.argtypes = [P, L, I, P, L, I, I, I, I, F, F, F, P, L, I, I, P]
     h.prb_route.argtypes = [P, P, P, P, L, P, P, I, I, I, I, I, P]
     h.prb_latent_prepare.argtypes = [P, L, P, P, L, I, I, P, P, P, P, P, I, I, I, I, I, I, I, F,
@@ -967,6 +969,22 @@ def rms_norm(x, out=None, x_out=None, y=None, gate=None, gate_bias=None, gain=No
                               float(alpha), float(eps), 1 if branch_only else 0,
                               dtype_code(out.dtype) if out is not None else F32, _p(status),
                               _stream()), what)
+
+
+def gate_mul(out, inp, gate) -> None:
+    """out[t, i] = inp[t, i] * sigmoid(gate[t, i]) for the columns of ``inp``; inp and gate
+    float32 (column slices of wider tensors are fine), out in the activation type with at least
+    as many columns."""
+    what = "gate_mul"
+    for name, t in (("inp", inp), ("gate", gate)):
+        if not t.is_cuda or t.dtype != torch.float32 or t.stride(1) != 1:
+            raise KernelArgumentError(f"{what}: {name} must be float32 on CUDA with unit inner stride")
+    n_rows, n = inp.shape
+    if gate.shape[0] < n_rows or gate.shape[1] < n or out.stride(1) != 1 or out.shape[0] < n_rows or \
+            out.shape[1] < n:
+        raise KernelArgumentError(f"{what}: shapes do not fit")
+    _check(lib().prb_gate_mul(_p(out), out.stride(0), _p(inp), inp.stride(0), _p(gate),
+                              gate.stride(0), n_rows, n, dtype_code(out.dtype), _stream()), what)
 
 
 def gated_pair(out, inp, gate_col: int, up_col: int, n: int, out_col: int = 0, limit: float = 0.0,

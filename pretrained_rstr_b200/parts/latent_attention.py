@@ -261,6 +261,18 @@ class LatentAttention(Mixer):
             self.uvt = v_up.to(dtype).reshape(self.heads, self.vdim, self.rank) \
                 .transpose(1, 2).contiguous()
             self.out = padded_linear(out, runtime)
+        self.uv_blocks = None
+        if self.tensor_cores and self.value_gate:
+            # for steps of many rows: all heads' Uv as ONE product with the matrices along the
+            # diagonal (heads times the needed arithmetic, on tensor cores, for a fraction of the
+            # per-head kernel's time); steps of few rows keep the per-head kernel, which reads
+            # the needed weights only
+            uvb = torch.zeros((self.heads * self.vdim, self.heads * self.rank), dtype=torch.float32,
+                              device=v_up.device)
+            for hh in range(self.heads):
+                uvb[hh * self.vdim:(hh + 1) * self.vdim, hh * self.rank:(hh + 1) * self.rank] = \
+                    v_up[hh * self.vdim:(hh + 1) * self.vdim].to(torch.float32)
+            self.uv_blocks = padded_linear(uvb, runtime)
         if not self.tensor_cores:
             self.q_up = padded_linear(q_up, runtime) if self.q_rank is not None else None
             self.uk = k_up.to(dtype).contiguous()
@@ -318,10 +330,17 @@ class LatentAttention(Mixer):
             qa = ctx.scratch("latent_qa", (cap, self.heads, width), dtype)[:t]
             first.forward(ctx, cq if latent_q else h, qa.view(t, self.heads * width))
             if self.value_gate:
-                lat = ctx.scratch("latent_sum", (cap, self.heads, self.rank), torch.float32)[:t]
-                self._attend_tensor_cores(ctx, lat, qa, cache, group, None)
                 o = ctx.scratch_zero("latent_o", (cap, self.out.n_in), dtype)[:t]
-                ops.latent_unfold(o, lat, self.uvt, gate, self.heads, self.rank, self.vdim)
+                if ctx.layout.t_cap > self.UNFOLD_ROWS:
+                    sums = ctx.scratch("latent_gated", (cap, self.heads, self.rank), dtype)[:t]
+                    self._attend_tensor_cores(ctx, sums, qa, cache, group, None)
+                    val = ctx.scratch("latent_values", (cap, self.heads * self.vdim), torch.float32)[:t]
+                    self.uv_blocks.forward(ctx, sums.view(t, self.heads * self.rank), val)
+                    ops.gate_mul(o, val, gate)
+                else:
+                    lat = ctx.scratch("latent_sum", (cap, self.heads, self.rank), torch.float32)[:t]
+                    self._attend_tensor_cores(ctx, lat, qa, cache, group, None)
+                    ops.latent_unfold(o, lat, self.uvt, gate, self.heads, self.rank, self.vdim)
                 self.out.forward(ctx, o, x, resid=x if accumulate else None)
                 return
             gated = ctx.scratch("latent_gated", (cap, self.heads, self.rank), dtype)[:t]
@@ -346,6 +365,9 @@ class LatentAttention(Mixer):
 
     #: most key ranges of a launch: single tokens, prompt tiles
     MAX_SPLITS = (32, 8)
+    #: steps with room for more token rows than this expand the values of all heads as one
+    #: product (a gate per value coordinate keeps Uv apart from the output projection)
+    UNFOLD_ROWS = 64
 
     def _attend_tensor_cores(self, ctx, lat, qa, cache: LayerCache, group, gate=None) -> None:
         """Single tokens and prompt tiles as two launches (each only if the step has such
