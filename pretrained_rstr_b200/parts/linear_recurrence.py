@@ -56,9 +56,16 @@ class GatedLinearRecurrence(Mixer):
             return t
 
         f32 = lambda t: t.to(torch.float32).contiguous()
-        self.input = FusedInput(self.width, runtime, "lru_in")
-        self.input.add("y", need("y", (self.inner, self.width)))
-        self.input.add("x", need("x", (self.inner, self.width)))
+        # the two projections: one product of the mixer's own, or rows in the product of a
+        # mixer beside it that reads the same input (``input_host``)
+        self.host = p.get("input_host")
+        self.input = None if self.host is not None else FusedInput(self.width, runtime, "lru_in")
+        for name in ("y", "x"):
+            rows = need(name, (self.inner, self.width))
+            if self.host is not None:
+                self.host.fuse_input_rows("lru_" + name, rows)
+            else:
+                self.input.add(name, rows)
         self.y_bias = f32(need("y_bias", (self.inner,))) if w.get("y_bias") else None
         self.x_bias = f32(need("x_bias", (self.inner,))) if w.get("x_bias") else None
         self.conv_w = f32(need("conv", (self.inner, self.taps)))
@@ -83,18 +90,18 @@ class GatedLinearRecurrence(Mixer):
         """State bytes a single token reads and writes back, whatever the context."""
         return 2 * 4 * self.inner * self.taps
 
-    def fuse_input_rows(self, name: str, weight) -> str:
-        return self.input.add(name, weight)
-
-    def fused_rows(self, name: str):
-        return self.input.view(self._proj, name)
+    takes_input_host = True
 
     def forward(self, ctx, h, x, cache: LayerCache, accumulate: bool = True) -> None:
         t = x.shape[0]
         cap = ctx.token_capacity
         state, inputs = cache.state["lru_state"], cache.state["lru_inputs"]
-        proj = self._proj = self.input.run(ctx, h)
-        cols = self.input.cols
+        if self.host is not None:
+            proj, host_cols = self.host.fused_product()
+            cols = {name: host_cols["lru_" + name] for name in ("y", "x")}
+        else:
+            proj = self._proj = self.input.run(ctx, h)
+            cols = self.input.cols
         gated = ctx.scratch_zero("lru_gated", (cap, self.out.n_in), self.runtime.dtype)[:t]
         requests = ctx.layout.b_cap
         if ctx.layout.t_cap <= ops.lru_segment() and self.one_launch:

@@ -59,10 +59,16 @@ class MatrixMemory(Mixer):
 
         hk, hv = self.heads * self.dim, self.heads * self.vdim
         f32 = lambda t: t.to(torch.float32).contiguous()
-        self.input = FusedInput(self.width, runtime, "mmem_in")
+        # the six projections: one product of the mixer's own, or rows in the product of a
+        # mixer beside it that reads the same input (``input_host``)
+        self.host = p.get("input_host")
+        self.input = None if self.host is not None else FusedInput(self.width, runtime, "mmem_in")
         for name, rows in (("q", hk), ("k", hk), ("v", hv), ("gate", hv), ("i", self.heads),
                            ("f", self.heads)):
-            self.input.add(name, need(name, (rows, self.width)))
+            if self.host is not None:
+                self.host.fuse_input_rows("mmem_" + name, need(name, (rows, self.width)))
+            else:
+                self.input.add(name, need(name, (rows, self.width)))
         self.i_bias = f32(need("i_bias", (self.heads,))) if w.get("i_bias") else None
         self.f_bias = f32(need("f_bias", (self.heads,))) if w.get("f_bias") else None
         self.norm = f32(need("norm", (hv,)))
@@ -78,17 +84,17 @@ class MatrixMemory(Mixer):
         """State bytes a single token reads and writes back, whatever the context."""
         return 2 * 4 * self.heads * (self.dim * self.vdim + self.dim + 1)
 
-    def fuse_input_rows(self, name: str, weight) -> str:
-        return self.input.add(name, weight)
-
-    def fused_rows(self, name: str):
-        return self.input.view(self._proj, name)
+    takes_input_host = True
 
     def forward(self, ctx, h, x, cache: LayerCache, accumulate: bool = True) -> None:
         t = x.shape[0]
         cap = ctx.token_capacity
-        proj = self._proj = self.input.run(ctx, h)
-        c = self.input.cols
+        if self.host is not None:
+            proj, host_cols = self.host.fused_product()
+            c = {name: host_cols["mmem_" + name] for name in ("q", "k", "v", "gate", "i", "f")}
+        else:
+            proj = self._proj = self.input.run(ctx, h)
+            c = self.input.cols
         gated = ctx.scratch_zero("mmem_gated", (cap, self.out.n_in), self.runtime.dtype)[:t]
         columns = (c["q"][0], c["k"][0], c["v"][0], c["i"][0], c["f"][0], c["gate"][0])
         states = (cache.state["mmem_s"], cache.state["mmem_n"], cache.state["mmem_m"])

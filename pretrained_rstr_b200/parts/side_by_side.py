@@ -3,7 +3,12 @@ scale_a * a(h) + scale_b * b(h).  The children are any registered mixers (``left
 are their :class:`~pretrained_rstr_b200.config.base.PartSpec`s); each gets its constant as
 ``out_scale``, applied in 32-bit before its output projection, and adds its projection to the
 stream itself.  At most one child may keep keys and values (the layer has one cache); the
-children's states are declared together (their names must differ)."""
+children's states are declared together (their names must differ).  Where the first child keeps
+its projections in one fused product and offers room in it (``fuse_input_rows``) and the second
+child can take its own from a host (``takes_input_host``), the second child's projections ride
+in the first child's product: one product a layer reads the stream for both (``input_host`` is
+offered to every second child; one that keeps a product of its own over another input ignores
+it).  ``share_product`` False keeps the products apart."""
 from __future__ import annotations
 
 from .interfaces import LayerCache, Mixer
@@ -17,7 +22,11 @@ class SideBySide(Mixer):
         self.children = []
         for side in ("left", "right"):
             spec = p[side]
-            scaled = type(spec)(spec.kind, {**spec.params, "out_scale": float(p.get(side + "_scale", 1.0))})
+            extra = {"out_scale": float(p.get(side + "_scale", 1.0))}
+            if self.children and hasattr(self.children[0], "fuse_input_rows") and \
+                    hasattr(self.children[0], "fused_product") and p.get("share_product", True):
+                extra["input_host"] = self.children[0]
+            scaled = type(spec)(spec.kind, {**spec.params, **extra})
             self.children.append(build_part("mixer", scaled, store, runtime))
         if sum(c.kv_spec() is not None for c in self.children) > 1:
             raise ValueError("side_by_side: only one of the two mixers may keep keys and values")

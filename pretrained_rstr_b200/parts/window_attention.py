@@ -136,6 +136,11 @@ class WindowAttention(Mixer):
     def fused_rows(self, name: str):
         return self.input.view(self._proj, name)
 
+    def fused_product(self):
+        """(the fused product's 32-bit result of this step, first column by segment name): for a
+        mixer beside this one whose projections ride in the product."""
+        return self._proj, self.input.cols
+
     def forward(self, ctx, h, x, cache: LayerCache, accumulate: bool = True) -> None:
         if self.shares_cache == cache.writes:
             raise ValueError("window_attention: a layer without key/value tensors reads another "
