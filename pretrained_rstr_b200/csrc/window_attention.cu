@@ -2,12 +2,15 @@
 // key/value heads, key and value heads of different sizes, a sliding window that may keep a
 // sequence's first tokens visible, a bias that grows with the distance of query and key, a
 // root-mean-square norm over the whole query (and key) projection, a query temperature that
-// grows with the position, rotary positions on a head's first coordinates, and a gate per head
-// on the result.  Every option is a parameter; a mixer that leaves one out passes 0 / null.
+// grows with the position, a norm per head before or after the rotation, biases, rotary
+// positions on a head's first coordinates, a learned sink per head in the softmax's
+// denominator, and a gate per head or per value coordinate on the result.  Every option is a
+// parameter; a mixer that leaves one out passes 0 / null.
 //
 //   visible(i, j) = j <= i and (i - j < window or j < keep_first)         (window 0: all j <= i)
 //   score(i, j)   = (q_i . k_j) * scale - slope_h * (i - j)
-//   o_i           = softmax_j(score) V * sigmoid(gate_i,h) * out_scale
+//   w(i, j)       = exp(score(i, j)) / (sum_j' exp(score(i, j')) + exp(sink_h))
+//   o_i           = (sum_j w(i, j) v_j) * sigmoid(gate_i,h or gate_i,h,c) * out_scale
 //
 // Cache: one pool per layer, one row per (token, key/value head): [k (dim) | v (vdim)], so a
 // key and its value come with one page look-up and their sizes need not be equal.
