@@ -141,10 +141,15 @@ class VakilornConfig(ModelConfig):
                         or src == i:
                     raise ConfigError(f"config.json: {where}.weights_of must name another layer, "
                                       f"got {src!r}")
+                seen = {i}
+                while isinstance(self.layers[src], dict) and self.layers[src].get("weights_of") is not None:
+                    seen.add(src)                 # (a layer that itself runs another's tensors)
+                    src = self.layers[src]["weights_of"]
+                    if isinstance(src, bool) or not isinstance(src, int) or \
+                            not 0 <= src < len(self.layers) or src in seen:
+                        raise ConfigError(f"config.json: {where}.weights_of leads to no layer with "
+                                          f"tensors of its own")
                 other = self.layers[src]
-                if other.get("weights_of") is not None:
-                    raise ConfigError(f"config.json: {where}.weights_of names layer {src}, which has "
-                                      f"no tensors of its own")
                 if not isinstance(other, dict) or other.get("type") != entry.get("type"):
                     raise ConfigError(f"config.json: {where} uses layer {src}'s tensors but "
                                       f"describes another layer")
@@ -281,14 +286,18 @@ class VakilornConfig(ModelConfig):
         """Layers in order; a layer with ``weights_of`` runs the parts of the layer it names with
         a cache and state of its own (caches are numbered by the listed layer)."""
         place = {i: k for k, i in enumerate(self.own_layers())}
-        return [RunEntry(place[i if e.get("weights_of") is None else e["weights_of"]], i)
-                for i, e in enumerate(self.layers)]
+        return [RunEntry(place[self.tensors_of(i)], i) for i in range(len(self.layers))]
+
+    def tensors_of(self, i: int) -> int:
+        """The layer whose tensors layer i runs: itself, or where its ``weights_of`` leads."""
+        while self.layers[i].get("weights_of") is not None:
+            i = self.layers[i]["weights_of"]
+        return i
 
     def layer_entry(self, i: int) -> Dict[str, Any]:
         """The entry whose sizes layer i runs with: its own, or, for a layer that runs another
         layer's tensors, that layer's (the tensors' shapes are that layer's)."""
-        src = self.layers[i].get("weights_of")
-        return self.layers[i if src is None else src]
+        return self.layers[self.tensors_of(i)]
 
     def embedding_spec(self) -> PartSpec:
         bg = self.embedding.get("bigram")

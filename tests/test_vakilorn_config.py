@@ -87,6 +87,17 @@ def test_bad_configurations_are_named(change, where):
     assert where in str(err.value)
 
 
+def test_a_chain_of_shared_layers_leads_to_the_owner():
+    raw = copy.deepcopy(RAW)
+    raw["layers"].append({**copy.deepcopy(_REC), "weights_of": 0})      # 4 -> 0 -> 2
+    cfg = lookup(raw).config_class.from_dict(raw)
+    assert [e.layer for e in cfg.run_order()] == [1, 0, 1, 2, 1]
+    assert [e.cache_layer for e in cfg.run_order()] == [0, 1, 2, 3, 4]
+    raw["layers"][2]["weights_of"] = 4                                    # a circle
+    with pytest.raises(ConfigError):
+        lookup(raw).config_class.from_dict(raw)
+
+
 def test_named_sizes_and_random_models(tmp_path):
     for name in ("vakilorn-tiny", "vakilorn-small", "vakilorn-wide"):
         arch, cfg = named_size(name)
