@@ -28,7 +28,10 @@ unfold through Uv with the gate, the output projection.  bfloat16 on tensor core
 folded into Uq and Uv into the output projection when the model is built (in 32-bit, rounded
 once), so a step is the folded query product, the attention kernel, which rotates the
 queries as it loads them and leaves the gated sums in bfloat16, and the folded output
-product: three kernels fewer, and the per-head matrices run at the products' speed.
+product: three kernels fewer, and the per-head matrices run at the products' speed.  With a
+gate per value coordinate Uv cannot move into the output projection (the gate acts between
+them): steps of few rows expand the values per head (``latent_unfold``), steps of many rows
+as one product with all heads' Uv along the diagonal, followed by the gate.
 
 The first matrix product carries Dq, Dkv and G in one, and whatever rows an arrangement
 asks to ride along (:meth:`fuse_input_rows`); its float32 result feeds the norms unrounded.
