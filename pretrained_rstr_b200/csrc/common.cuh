@@ -87,6 +87,20 @@ __device__ __forceinline__ float prb_block_max(float v, float* scratch) {
     return r;
 }
 
+// Sine and cosine of position x frequency (rotary positions).  The product and its reduction
+// to one turn are taken in 64-bit: a 32-bit product at position p is off by up to p * 2^-24
+// radians, independently for a query and a key, which at positions in the thousands is the
+// largest error of a 32-bit step.
+__device__ __forceinline__ void prb_sincos_angle(float pos, float freq, float* sn, float* cs,
+                                                 float freq_lo = 0.0f) {
+    // (freq_lo: what the frequency's own rounding to 32 bits left out, where the caller has it:
+    // over a distance of d positions it is worth d * 2^-25 radians)
+    double s, c;
+    sincos((double)pos * ((double)freq + (double)freq_lo), &s, &c);
+    *sn = (float)s;
+    *cs = (float)c;
+}
+
 // activation codes
 #define PRB_ACT_NONE 0
 #define PRB_ACT_GELU_TANH 1

@@ -13,7 +13,8 @@
 //   prb_latent_unfold    Uv_h (.) per head, times sigmoid(gate) per head
 //
 // Rotation: the first `rot_dims` coordinates of the rotated part in the rotate-half layout,
-// coordinate i with i + rot_dims/2 by the angle position * freq[i]; 32-bit.  Scores, softmax
+// coordinate i with i + rot_dims/2 by the angle position * freq[i] (the product in 64-bit,
+// with freq_lo[i], the part of the frequency that 32 bits leave out, where given).  Scores, softmax
 // weights, norms and all sums are 32-bit; the cache and the weights are float32 or bfloat16.
 // Sums run over keys, and over a head's coordinates, in an order that depends on the position
 // only, never on the rest of the batch.
@@ -42,7 +43,7 @@ latent_prepare_kernel(A* __restrict__ cq, long cq_ld, C* __restrict__ cache,
                       const int* __restrict__ slots, const int* __restrict__ positions,
                       const float* __restrict__ freq, int n_tokens, int q_rank, int rank,
                       int rot_dim, int rot_dims, int page_size, int num_pages, float eps,
-                      float rot_scale, int* status) {
+                      float rot_scale, const float* __restrict__ freq_lo, int* status) {
     __shared__ float scratch[32];
     prb_grid_launch_dependents();          // (a product that follows may set itself up meanwhile)
     const int t = blockIdx.x;
@@ -77,11 +78,11 @@ latent_prepare_kernel(A* __restrict__ cq, long cq_ld, C* __restrict__ cache,
         float v = r[i];
         if (i < half) {
             float sn, cs;
-            sincosf(pos * freq[i], &sn, &cs);
+            prb_sincos_angle(pos, freq[i], &sn, &cs, freq_lo ? freq_lo[i] : 0.0f);
             v = (r[i] * cs - r[i + half] * sn) * rot_scale;
         } else if (i < rot_dims) {
             float sn, cs;
-            sincosf(pos * freq[i - half], &sn, &cs);
+            prb_sincos_angle(pos, freq[i - half], &sn, &cs, freq_lo ? freq_lo[i - half] : 0.0f);
             v = (r[i] * cs + r[i - half] * sn) * rot_scale;
         }
         row[rank + i] = prb_from_float<C>(v);
@@ -99,8 +100,8 @@ template <typename W, typename O>
 __global__ void __launch_bounds__(LA_THREADS)
 latent_fold_kernel(O* __restrict__ qa, const float* __restrict__ q, long ld,
                    const W* __restrict__ uk, const int* __restrict__ positions,
-                   const float* __restrict__ freq, int n_tokens, int heads, int dim, int rot_dim,
-                   int rot_dims, int rank) {
+                   const float* __restrict__ freq, const float* __restrict__ freq_lo, int n_tokens,
+                   int heads, int dim, int rot_dim, int rot_dims, int rank) {
     extern __shared__ float qs[];                        // [LA_GROUP][dim]
     __shared__ float part[LA_SLICES][LA_GROUP][LA_OUT];
     const int t0 = blockIdx.x * LA_GROUP, h = blockIdx.y;
@@ -116,11 +117,11 @@ latent_fold_kernel(O* __restrict__ qa, const float* __restrict__ q, long ld,
             float v = r[i];
             if (i < half) {
                 float sn, cs;
-                sincosf(pos * freq[i], &sn, &cs);
+                prb_sincos_angle(pos, freq[i], &sn, &cs, freq_lo ? freq_lo[i] : 0.0f);
                 v = r[i] * cs - r[i + half] * sn;
             } else if (i < rot_dims) {
                 float sn, cs;
-                sincosf(pos * freq[i - half], &sn, &cs);
+                prb_sincos_angle(pos, freq[i - half], &sn, &cs, freq_lo ? freq_lo[i - half] : 0.0f);
                 v = r[i] * cs + r[i - half] * sn;
             }
             qa[((size_t)t * heads + h) * D + rank + i] = prb_from_float<O>(v);
@@ -307,7 +308,8 @@ PRB_API int prb_latent_prepare(void* cq, long cq_ld, void* cache, const float* p
                                const int* slots, const int* positions, const float* freq,
                                int n_tokens, int q_rank, int rank, int rot_dim, int rot_dims,
                                int page_size, int num_pages, float eps, int cache_dtype,
-                               int act_dtype, float rot_scale, int* status, cudaStream_t stream) {
+                               int act_dtype, float rot_scale, const float* freq_lo, int* status,
+                               cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (rank <= 0 || rot_dim < 0 || rot_dims < 0 || rot_dims > rot_dim || rot_dims % 2 != 0 ||
         page_size <= 0 || (cq != nullptr && q_rank <= 0))
@@ -315,7 +317,8 @@ PRB_API int prb_latent_prepare(void* cq, long cq_ld, void* cache, const float* p
 #define PRB_LP(C, A)                                                                              \
     latent_prepare_kernel<C, A><<<dim3(n_tokens, 2), LA_THREADS, 0, stream>>>(                    \
         (A*)cq, cq_ld, (C*)cache, proj, ld, q_col, kv_col, wq, wkv, slots, positions, freq,       \
-        n_tokens, q_rank, rank, rot_dim, rot_dims, page_size, num_pages, eps, rot_scale, status)
+        n_tokens, q_rank, rank, rot_dim, rot_dims, page_size, num_pages, eps, rot_scale, freq_lo,  \
+        status)
     if (cache_dtype == PRB_F32 && act_dtype == PRB_F32) PRB_LP(float, float);
     else if (cache_dtype == PRB_BF16 && act_dtype == PRB_BF16) PRB_LP(__nv_bfloat16, __nv_bfloat16);
     else if (cache_dtype == PRB_BF16 && act_dtype == PRB_F32) PRB_LP(__nv_bfloat16, float);
@@ -327,9 +330,9 @@ PRB_API int prb_latent_prepare(void* cq, long cq_ld, void* cache, const float* p
 }
 
 PRB_API int prb_latent_fold(void* qa, const float* q, long ld, const void* uk,
-                            const int* positions, const float* freq, int n_tokens, int heads,
-                            int dim, int rot_dim, int rot_dims, int rank, int w_dtype,
-                            int out_dtype, cudaStream_t stream) {
+                            const int* positions, const float* freq, const float* freq_lo,
+                            int n_tokens, int heads, int dim, int rot_dim, int rot_dims, int rank,
+                            int w_dtype, int out_dtype, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (heads <= 0 || heads > 65535 || dim <= 0 || rank <= 0 || rot_dim < 0 || rot_dims > rot_dim ||
         rot_dims % 2 != 0)
@@ -339,16 +342,16 @@ PRB_API int prb_latent_fold(void* qa, const float* q, long ld, const void* uk,
     dim3 grid((n_tokens + LA_GROUP - 1) / LA_GROUP, heads, (rank + LA_OUT - 1) / LA_OUT + 1);
     if (w_dtype == PRB_F32 && out_dtype == PRB_F32)
         latent_fold_kernel<float, float><<<grid, LA_THREADS, smem, stream>>>(
-            (float*)qa, q, ld, (const float*)uk, positions, freq, n_tokens, heads, dim, rot_dim,
-            rot_dims, rank);
+            (float*)qa, q, ld, (const float*)uk, positions, freq, freq_lo, n_tokens, heads, dim,
+            rot_dim, rot_dims, rank);
     else if (w_dtype == PRB_BF16 && out_dtype == PRB_F32)
         latent_fold_kernel<__nv_bfloat16, float><<<grid, LA_THREADS, smem, stream>>>(
-            (float*)qa, q, ld, (const __nv_bfloat16*)uk, positions, freq, n_tokens, heads, dim,
-            rot_dim, rot_dims, rank);
+            (float*)qa, q, ld, (const __nv_bfloat16*)uk, positions, freq, freq_lo, n_tokens, heads,
+            dim, rot_dim, rot_dims, rank);
     else if (w_dtype == PRB_BF16 && out_dtype == PRB_BF16)
         latent_fold_kernel<__nv_bfloat16, __nv_bfloat16><<<grid, LA_THREADS, smem, stream>>>(
-            (__nv_bfloat16*)qa, q, ld, (const __nv_bfloat16*)uk, positions, freq, n_tokens, heads,
-            dim, rot_dim, rot_dims, rank);
+            (__nv_bfloat16*)qa, q, ld, (const __nv_bfloat16*)uk, positions, freq, freq_lo, n_tokens,
+            heads, dim, rot_dim, rot_dims, rank);
     else
         return PRB_E_DTYPE;
     PRB_LAUNCH_CHECK();

@@ -139,8 +139,8 @@ def _declare(h: ctypes.CDLL) -> None:
     h.prb_gated_pair.argtypes = [P, L, I, P, L, I, I, I, I, F, F, F, P, L, I, I, P]
     h.prb_route.argtypes = [P, P, P, P, L, P, P, I, I, I, I, I, P]
     h.prb_latent_prepare.argtypes = [P, L, P, P, L, I, I, P, P, P, P, P, I, I, I, I, I, I, I, F,
-                                     I, I, F, P, P]
-    h.prb_latent_fold.argtypes = [P, P, L, P, P, P, I, I, I, I, I, I, I, I, P]
+                                     I, I, F, P, P, P]
+    h.prb_latent_fold.argtypes = [P, P, L, P, P, P, P, I, I, I, I, I, I, I, I, P]
     h.prb_latent_attention_mma.argtypes = [P, P, P, L, P, P, P, P, P, P, P, P, I, P, P, P, I, I, I,
                                            I, I, I, F, I, I, I, I, I, P, I, P, P]
     h.prb_latent_mma_supports.argtypes = [I, I, I]
@@ -190,7 +190,7 @@ def _declare(h: ctypes.CDLL) -> None:
                                          I, I, I, I, I, I, I, I, I, P, P, P, I, P, P]
     h.prb_tmix_finish.argtypes = [P, L, P, L, P, L, I, P, P, I, I, I, F, F, I, P]
     h.prb_wattn_prepare.argtypes = [P, P, P, L, I, I, I, P, P, P, P, P, I, I, I, I, I, I, F, F, I,
-                                    I, I, I, I, P, P, P, P, P]
+                                    I, I, I, I, P, P, P, P, P, P]
     h.prb_wattn.argtypes = [P, L, P, P, P, P, P, P, L, P, I, I, I, I, I, I, I, I, I, I, F, F, I, I,
                             P, I, P, P]
     h.prb_wattn_tile_rows.argtypes = [I, I, I, I]
@@ -1039,7 +1039,7 @@ def route(scale, chosen, chosen_w, x, w, bias, top: int) -> None:
 # ----------------------------------------------------- attention over a shared latent
 def latent_prepare(cq, cache, proj, q_col: int, kv_col: int, wq, wkv, slots, positions, freq,
                    q_rank: int, rank: int, rot_dim: int, rot_dims: int, eps: float, status,
-                   rot_scale: float = 1.0) -> None:
+                   rot_scale: float = 1.0, freq_lo=None) -> None:
     """Per token: the query latent proj[t, q_col : q_col + q_rank], unit-RMS-normed with weight
     ``wq``, goes to ``cq`` ([T, >= q_rank], activation type); the key/value latent
     proj[t, kv_col : kv_col + rank], normed with ``wkv``, and the ``rot_dim`` columns after it,
@@ -1073,11 +1073,22 @@ def latent_prepare(cq, cache, proj, q_col: int, kv_col: int, wq, wkv, slots, pos
                                     rot_dims, page_size, num_pages, float(eps),
                                     dtype_code(cache.dtype),
                                     dtype_code(cache.dtype if cq is None else cq.dtype),
-                                    float(rot_scale), _p(status), _stream()), what)
+                                    float(rot_scale), _p(_freq_lo(freq_lo, rot_dims, what)),
+                                    _p(status), _stream()), what)
+
+
+def _freq_lo(freq_lo, rot_dims: int, what: str):
+    """``freq_lo``: float32, one number per rotated pair: what each frequency's rounding to 32
+    bits left out (the kernels add it to the frequency in 64-bit); None: nothing."""
+    if freq_lo is not None:
+        _need(freq_lo, torch.float32, "freq_lo", what)
+        if freq_lo.numel() < rot_dims // 2:
+            raise KernelArgumentError(f"{what}: {rot_dims // 2} low parts of frequencies wanted")
+    return freq_lo
 
 
 def latent_fold(qa, q, uk, positions, freq, heads: int, dim: int, rot_dim: int, rot_dims: int,
-                rank: int) -> None:
+                rank: int, freq_lo=None) -> None:
     """qa[t, h, :rank] = Uk_h^T q[t, h, :dim]; qa[t, h, rank:] = q[t, h, dim:] rotated by the
     token's position.  q float32 [T, heads * (dim + rot_dim)]; uk [heads * dim, rank];
     qa [T, heads, rank + rot_dim], float32 or bfloat16."""
@@ -1089,7 +1100,7 @@ def latent_fold(qa, q, uk, positions, freq, heads: int, dim: int, rot_dim: int, 
     if tuple(uk.shape) != (heads * dim, rank) or tuple(qa.shape) != (q.shape[0], heads, rank + rot_dim):
         raise KernelArgumentError(f"{what}: shapes do not fit")
     _check(lib().prb_latent_fold(_p(qa), _p(q), q.stride(0), _p(uk), _p(positions), _p(freq),
-                                 q.shape[0], heads, dim, rot_dim, rot_dims, rank,
+                                 _p(_freq_lo(freq_lo, rot_dims, what)), q.shape[0], heads, dim, rot_dim, rot_dims, rank,
                                  dtype_code(uk.dtype), dtype_code(qa.dtype), _stream()), what)
 
 
@@ -1657,7 +1668,7 @@ def tmix_finish(out, raw, proj, g_col: int, norm_w, seq_of_token, heads: int, vd
 def wattn_prepare(q_out, cache, proj, q_col: int, k_col: int, v_col: int, q_norm, k_norm, slots,
                   positions, freq, heads: int, kv_heads: int, dim: int, vdim: int, rot_dims: int,
                   eps: float, temp_coef: float, temp_every: int, status=None, head_norm=None,
-                  biases=None) -> None:
+                  biases=None, freq_lo=None) -> None:
     """Queries and keys of the step's tokens as the attention reads them: a root-mean-square
     norm over the whole projection (``q_norm`` / ``k_norm``: float32 weights, or None), or per
     head (``head_norm`` "before": before the rotation, ``q_norm`` / ``k_norm`` of ``dim`` numbers
@@ -1707,7 +1718,8 @@ def wattn_prepare(q_out, cache, proj, q_col: int, k_col: int, v_col: int, q_norm
                                    _p(positions), _p(freq), n, heads, kv_heads, dim, vdim,
                                    int(rot_dims), float(eps), float(temp_coef), int(temp_every),
                                    page_size, pages, dtype_code(cache.dtype), mode, _p(bq),
-                                   _p(bk), _p(bv), _p(status), _stream()), what)
+                                   _p(bk), _p(bv), _p(_freq_lo(freq_lo, rot_dims, what)),
+                                   _p(status), _stream()), what)
 
 
 def wattn_tile_rows(heads: int, kv_heads: int, dim: int, vdim: int) -> int:
@@ -1816,8 +1828,8 @@ def lru_conv(u, proj, x_col: int, x_bias, conv_w, conv_b, conv_state, seq_of_tok
 
 def lru_gates(a_out, u, wa_t, wi_t, ba, bi, decay, blocks: int) -> None:
     """Per token and block b of the channels: r = sigmoid(A_b u_b + ba), i = sigmoid(B_b u_b +
-    bi) (``wa_t`` / ``wi_t``: [blocks, in, out], the block matrices transposed), a = exp(decay
-    * r) to ``a_out`` and sqrt(1 - a^2) * i * u in place of u; 32-bit arithmetic."""
+    bi) (``wa_t`` / ``wi_t``: [blocks, in, out], the block matrices transposed), log a = decay * r
+    to ``a_out`` and sqrt(1 - a^2) * i * u in place of u; 32-bit arithmetic."""
     what = "lru_gates"
     _need(a_out, torch.float32, "a_out", what)
     _need(u, torch.float32, "u", what)
@@ -1889,8 +1901,9 @@ def lru_step(out, proj, y_col: int, x_col: int, y_bias, x_bias, conv_w, conv_b, 
 def lru_scan(out, a_in, inp, proj, y_col: int, x_col: int, y_bias, x_bias, state, conv_state,
              q_start, state_slot, positions, n_requests: int, out_scale: float = 1.0,
              segments=None) -> None:
-    """S_t = a_t S_(t-1) + inp_t per (request, channel) from and to ``state`` [slots, width]
-    (zero at position 0); out[t, c] = S_t * gelu_tanh(proj[t, y_col + c] + y_bias[c]) *
+    """S_t = a_t S_(t-1) + inp_t per (request, channel), with ``a_in`` holding log a_t (the
+    step is taken as S + (inp - (1 - a) S) with 1 - a = -expm1(log a), which keeps a decay
+    close to one exact), from and to ``state`` [slots, width] (zero at position 0); out[t, c] = S_t * gelu_tanh(proj[t, y_col + c] + y_bias[c]) *
     out_scale; ``conv_state`` then holds the request's last taps - 1 inputs proj[:, x_col + c] +
     x_bias[c].  ``segments`` = (own, keep), two float32 workspaces [n, width] for n >=
     lru_max_segments: portions run in segments of 64 tokens side by side (two launches)."""

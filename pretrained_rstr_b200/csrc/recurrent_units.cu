@@ -10,7 +10,7 @@
 //       out_t = S_t * gelu_tanh(y_t)
 //     lru_conv (a CTA per token; the taps before a portion's first token come from the
 //     request's saved inputs), lru_gates (a CTA per (8 tokens, block): the two block matrices
-//     in 32-bit FMA, a_t and the recurrence's input), lru_scan (a thread per (request,
+//     in 32-bit FMA, log a_t and the recurrence's input), lru_scan (a thread per (request,
 //     channel) walks the request's tokens in order from and to the state slot, multiplies by
 //     the other branch and brings the saved inputs up to date).
 //
@@ -31,6 +31,14 @@
 namespace {
 __device__ __forceinline__ float ru_sigmoid(float z) { return 1.0f / (1.0f + expf(-z)); }
 __device__ __forceinline__ float ru_logsigmoid(float z) { return fminf(z, 0.0f) - log1pf(expf(-fabsf(z))); }
+
+// One step of S <- a S + input, given log a.  A decay close to one, rounded to 32 bits, is off
+// by up to 3e-8, which is a relative error of 3e-8 / (1 - a) in how fast the state fades: over
+// a thousand tokens at a = 0.999 a far token's weight would be off by 3e-5.  1 - a = -expm1(log
+// a) keeps its full relative precision, so the step is taken as S + (input - (1 - a) S).
+__device__ __forceinline__ float lru_decay(float s, float log_a, float input) {
+    return s + fmaf(expm1f(log_a), s, input);
+}
 
 // ------------------------------------------------------------------ (1) convolution
 // conv_state: [slots, taps - 1, width], the branch's inputs (bias added) at the request's last
@@ -73,7 +81,7 @@ __global__ void lru_conv_kernel(float* __restrict__ u, const float* __restrict__
 
 // ------------------------------------------------------------------------ (1) gates
 constexpr int LRU_TOK = 8;
-// wa_t, wi_t: [blocks, bw (in), bw (out)]; a_out[t, c] = a_t; u[t, c] <- sqrt(1 - a^2) * i * u.
+// wa_t, wi_t: [blocks, bw (in), bw (out)]; a_out[t, c] = log a_t; u[t, c] <- sqrt(1 - a^2) * i * u.
 template <typename W>
 __global__ void __launch_bounds__(128)
 lru_gates_kernel(float* __restrict__ a_out, float* __restrict__ u, const W* __restrict__ wa_t,
@@ -113,9 +121,8 @@ lru_gates_kernel(float* __restrict__ a_out, float* __restrict__ u, const W* __re
             if (k >= nt) break;
             const float r = ru_sigmoid(ra[k] + bac), g = ru_sigmoid(ri[k] + bic);
             const float la = dc * r;                             // log a <= 0
-            const float a = expf(la);
             const float in = sqrtf(fmaxf(-expm1f(2.0f * la), 0.0f)) * g * us[k * bw + o];
-            a_out[(size_t)(t0 + k) * width + c] = a;
+            a_out[(size_t)(t0 + k) * width + c] = la;            // (the logarithm: see lru_decay)
             u[(size_t)(t0 + k) * width + c] = in;
         }
     }
@@ -144,7 +151,7 @@ lru_scan_kernel(O* __restrict__ out, long out_ld, const float* __restrict__ a_in
     const float yb = y_bias ? y_bias[c] : 0.0f;
 #pragma unroll 4
     for (int r = r0; r < r1; ++r) {
-        s = fmaf(a_in[(size_t)r * width + c], s, in[(size_t)r * width + c]);
+        s = lru_decay(s, a_in[(size_t)r * width + c], in[(size_t)r * width + c]);
         const float y = prb_activate(proj[(size_t)r * ld + y_col + c] + yb, PRB_ACT_GELU_TANH);
         out[(size_t)r * out_ld + c] = prb_from_float<O>(s * y * out_scale);
     }
@@ -257,7 +264,7 @@ __global__ void lru_step_kernel(LruStepArgs g) {
             const float r = ru_sigmoid(ra[k] + bac), gi = ru_sigmoid(ri[k] + bic);
             const float la = dc * r;
             const float in = sqrtf(fmaxf(-expm1f(2.0f * la), 0.0f)) * gi * us[k * bw + o];
-            s = fmaf(expf(la), s, in);
+            s = lru_decay(s, la, in);
             const float y = prb_activate(g.proj[(size_t)(tb + k) * g.ld + g.y_col + c] + yb, PRB_ACT_GELU_TANH);
             out[(size_t)(tb + k) * g.out_ld + c] = prb_from_float<O>(s * y * g.out_scale);
         }
@@ -290,7 +297,7 @@ __global__ void lru_step_kernel(LruStepArgs g) {
 // ------------------------------------------------- (1) long portions: the scan in segments
 // Segment z of the launch is segment s of request b (numbered in request order).  Pass 1: a
 // thread per (segment, channel) builds, from zero, what the segment's own tokens leave and the
-// product of its decays.  Pass 2: a thread per (segment, channel) first walks the request's
+// logarithm of the product of its decays.  Pass 2: a thread per (segment, channel) first walks the request's
 // earlier segments, U <- product U + own from the carried state, then runs its own tokens with
 // outputs; a request's last segment leaves the state and the saved inputs in the slot.
 constexpr int LRU_SEG = 64;
@@ -319,12 +326,12 @@ lru_seg_own_kernel(float* __restrict__ seg_own, float* __restrict__ seg_keep,
     const int c = blockIdx.y * blockDim.x + threadIdx.x;
     if (c >= width || s == nseg - 1) return;         // (a last segment's own sum is never needed)
     const int t0 = q_start[b] + s * LRU_SEG, t1 = min(min(q_start[b + 1], n_tokens), t0 + LRU_SEG);
-    float own = 0.0f, keep = 1.0f;
+    float own = 0.0f, keep = 0.0f;                   // (keep: the LOGARITHM of the decays' product)
 #pragma unroll 8
     for (int r = t0; r < t1; ++r) {
-        const float a = a_in[(size_t)r * width + c];
-        own = fmaf(a, own, in[(size_t)r * width + c]);
-        keep *= a;
+        const float la = a_in[(size_t)r * width + c];
+        own = lru_decay(own, la, in[(size_t)r * width + c]);
+        keep += la;
     }
     seg_own[(size_t)blockIdx.x * width + c] = own;
     seg_keep[(size_t)blockIdx.x * width + c] = keep;
@@ -352,12 +359,12 @@ lru_seg_scan_kernel(O* __restrict__ out, long out_ld, const float* __restrict__ 
     const int p0 = positions[r0];
     float s = (p0 > 0 && has_slot) ? state[(size_t)slot * width + c] : 0.0f;
     for (int z = 0; z < sg; ++z)
-        s = fmaf(seg_keep[(size_t)(base + z) * width + c], s, seg_own[(size_t)(base + z) * width + c]);
+        s = lru_decay(s, seg_keep[(size_t)(base + z) * width + c], seg_own[(size_t)(base + z) * width + c]);
     const int t0 = r0 + sg * LRU_SEG, t1 = min(r1, t0 + LRU_SEG);
     const float yb = y_bias ? y_bias[c] : 0.0f;
 #pragma unroll 8
     for (int r = t0; r < t1; ++r) {
-        s = fmaf(a_in[(size_t)r * width + c], s, in[(size_t)r * width + c]);
+        s = lru_decay(s, a_in[(size_t)r * width + c], in[(size_t)r * width + c]);
         const float y = prb_activate(proj[(size_t)r * ld + y_col + c] + yb, PRB_ACT_GELU_TANH);
         out[(size_t)r * out_ld + c] = prb_from_float<O>(s * y * out_scale);
     }

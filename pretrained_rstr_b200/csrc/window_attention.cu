@@ -59,7 +59,8 @@ template <typename D, typename F>
 __device__ __forceinline__ void wa_project(const float* __restrict__ src, int n_heads, int dim,
                                            int rot_dims, const float* __restrict__ norm_w,
                                            float eps, float factor, float pos,
-                                           const float* __restrict__ freq, float* scratch, F dst) {
+                                           const float* __restrict__ freq,
+                                           const float* __restrict__ freq_lo, float* scratch, F dst) {
     float inv = factor;
     if (norm_w != nullptr) {
         float ss = 0.0f;
@@ -76,7 +77,7 @@ __device__ __forceinline__ void wa_project(const float* __restrict__ src, int n_
         D* d = dst(hd);
         if (w < half) {
             float sn, cs;
-            sincosf(pos * freq[w], &sn, &cs);
+            prb_sincos_angle(pos, freq[w], &sn, &cs, freq_lo ? freq_lo[w] : 0.0f);
             const float a = s[w] * inv * (nw ? nw[w] : 1.0f);
             const float b = s[w + half] * inv * (nw ? nw[w + half] : 1.0f);
             d[w] = prb_from_float<D>(a * cs - b * sn);
@@ -98,7 +99,8 @@ __device__ __forceinline__ void wa_project_heads(const float* __restrict__ src,
                                                  int dim, int rot_dims, int norm_mode,
                                                  const float* __restrict__ norm_w, float eps,
                                                  float factor, float pos,
-                                                 const float* __restrict__ freq, F dst) {
+                                                 const float* __restrict__ freq,
+                                                 const float* __restrict__ freq_lo, F dst) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
     const int half = rot_dims / 2;
     const int units = half + (dim - rot_dims);
@@ -118,7 +120,7 @@ __device__ __forceinline__ void wa_project_heads(const float* __restrict__ src,
             for (int u = lane; u < units; u += 32) {
                 if (u < half) {
                     float sn, cs;
-                    sincosf(pos * freq[u], &sn, &cs);
+                    prb_sincos_angle(pos, freq[u], &sn, &cs, freq_lo ? freq_lo[u] : 0.0f);
                     const float a = s[u] + (bb ? bb[u] : 0.0f);
                     const float b = s[u + half] + (bb ? bb[u + half] : 0.0f);
                     const float ra = a * cs - b * sn, rb = b * cs + a * sn;
@@ -138,7 +140,7 @@ __device__ __forceinline__ void wa_project_heads(const float* __restrict__ src,
         for (int u = lane; u < units; u += 32) {
             if (u < half) {
                 float sn, cs;
-                sincosf(pos * freq[u], &sn, &cs);
+                prb_sincos_angle(pos, freq[u], &sn, &cs, freq_lo ? freq_lo[u] : 0.0f);
                 const float a = (s[u] + (bb ? bb[u] : 0.0f)) * pre * (nw ? nw[u] : 1.0f);
                 const float b = (s[u + half] + (bb ? bb[u + half] : 0.0f)) * pre * (nw ? nw[u + half] : 1.0f);
                 d[u] = prb_from_float<D>((a * cs - b * sn) * post);
@@ -162,7 +164,8 @@ __global__ void wattn_prepare_kernel(float* __restrict__ q_out, C* __restrict__ 
                                      float temp_coef, int temp_every, int page_size, int num_pages,
                                      int norm_mode, const float* __restrict__ q_bias,
                                      const float* __restrict__ k_bias,
-                                     const float* __restrict__ v_bias, int* status) {
+                                     const float* __restrict__ v_bias,
+                                     const float* __restrict__ freq_lo, int* status) {
     __shared__ float scratch[32];
     prb_grid_launch_dependents();
     const int t = blockIdx.x;
@@ -176,9 +179,9 @@ __global__ void wattn_prepare_kernel(float* __restrict__ q_out, C* __restrict__ 
     const bool per_head = norm_mode >= 2 || q_bias != nullptr || k_bias != nullptr;
     if (per_head)
         wa_project_heads<float>(row + q_col, q_bias, heads, dim, rot_dims, norm_mode, q_norm, eps,
-                                temp, pos, freq, [&](int hd) { return qo + hd * dim; });
+                                temp, pos, freq, freq_lo, [&](int hd) { return qo + hd * dim; });
     else
-        wa_project<float>(row + q_col, heads, dim, rot_dims, q_norm, eps, temp, pos, freq, scratch,
+        wa_project<float>(row + q_col, heads, dim, rot_dims, q_norm, eps, temp, pos, freq, freq_lo, scratch,
                           [&](int hd) { return qo + hd * dim; });
     if (slots == nullptr) return;
     const int slot = slots[t];
@@ -193,9 +196,9 @@ __global__ void wattn_prepare_kernel(float* __restrict__ q_out, C* __restrict__ 
     const size_t head_step = (size_t)page_size * rowlen;
     if (per_head)
         wa_project_heads<C>(row + k_col, k_bias, kv_heads, dim, rot_dims, norm_mode, k_norm, eps,
-                            1.0f, pos, freq, [&](int hd) { return base + hd * head_step; });
+                            1.0f, pos, freq, freq_lo, [&](int hd) { return base + hd * head_step; });
     else
-        wa_project<C>(row + k_col, kv_heads, dim, rot_dims, k_norm, eps, 1.0f, pos, freq, scratch,
+        wa_project<C>(row + k_col, kv_heads, dim, rot_dims, k_norm, eps, 1.0f, pos, freq, freq_lo, scratch,
                       [&](int hd) { return base + hd * head_step; });
     for (int u = threadIdx.x; u < kv_heads * vdim; u += blockDim.x) {
         const int g = u / vdim, j = u - g * vdim;
@@ -819,8 +822,8 @@ PRB_API int prb_wattn_prepare(float* q_out, void* cache, const float* proj, long
                               int n_tokens, int heads, int kv_heads, int dim, int vdim, int rot_dims,
                               float eps, float temp_coef, int temp_every, int page_size,
                               int num_pages, int cache_dtype, int norm_mode, const float* q_bias,
-                              const float* k_bias, const float* v_bias, int* status,
-                              cudaStream_t stream) {
+                              const float* k_bias, const float* v_bias, const float* freq_lo,
+                              int* status, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (norm_mode < 0 || norm_mode > 3) return PRB_E_ARG;
     if (heads <= 0 || kv_heads <= 0 || dim <= 0 || vdim <= 0 || rot_dims < 0 || rot_dims % 2 ||
@@ -830,12 +833,12 @@ PRB_API int prb_wattn_prepare(float* q_out, void* cache, const float* proj, long
         wattn_prepare_kernel<float><<<n_tokens, 256, 0, stream>>>(
             q_out, (float*)cache, proj, ld, q_col, k_col, v_col, q_norm, k_norm, slots, positions,
             freq, n_tokens, heads, kv_heads, dim, vdim, rot_dims, eps, temp_coef, temp_every,
-            page_size, num_pages, norm_mode, q_bias, k_bias, v_bias, status);
+            page_size, num_pages, norm_mode, q_bias, k_bias, v_bias, freq_lo, status);
     else if (cache_dtype == PRB_BF16)
         wattn_prepare_kernel<__nv_bfloat16><<<n_tokens, 256, 0, stream>>>(
             q_out, (__nv_bfloat16*)cache, proj, ld, q_col, k_col, v_col, q_norm, k_norm, slots,
             positions, freq, n_tokens, heads, kv_heads, dim, vdim, rot_dims, eps, temp_coef,
-            temp_every, page_size, num_pages, norm_mode, q_bias, k_bias, v_bias, status);
+            temp_every, page_size, num_pages, norm_mode, q_bias, k_bias, v_bias, freq_lo, status);
     else
         return PRB_E_DTYPE;
     PRB_LAUNCH_CHECK();

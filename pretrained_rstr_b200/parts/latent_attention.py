@@ -285,13 +285,14 @@ class LatentAttention(Mixer):
         yarn = p.get("rot_scaling")
         if yarn:
             from .positions_rotary import yarn_frequencies
-            self.freq, mag = yarn_frequencies(base, self.rot_dims, float(yarn["factor"]),
-                                              float(yarn["original"]), float(yarn["fast"]),
-                                              float(yarn["slow"]), dev)
+            (self.freq, self.freq_lo), mag = yarn_frequencies(
+                base, self.rot_dims, float(yarn["factor"]), float(yarn["original"]),
+                float(yarn["fast"]), float(yarn["slow"]), dev, with_lo=True)
             self.rot_scale = mag * mag         # both sides' magnitudes, on the cached key part
         else:
-            self.freq = torch.tensor([base ** (-2.0 * i / self.rot_dims) for i in range(half)] or [0.0],
-                                     dtype=torch.float64).to(torch.float32).to(dev)
+            from .positions_rotary import split_frequencies
+            self.freq, self.freq_lo = split_frequencies(
+                [base ** (-2.0 * i / self.rot_dims) for i in range(half)] or [0.0], dev)
         self.work_plan = LatentWork()
         self.tile_tokens = self.work_plan.note_mixer(self.heads)
         self.sm_count = ops.sm_count() if torch.cuda.is_available() else 148
@@ -324,7 +325,8 @@ class LatentAttention(Mixer):
         ops.latent_prepare(cq, cache.k, proj, cols["q"][0] if latent_q else 0, cols["kv"][0],
                            self.q_norm, self.kv_norm, group.slots if cache.writes else None,
                            ctx.positions, self.freq, self.q_rank or 0, self.rank, self.rot_dim,
-                           self.rot_dims, self.eps, ctx.status, rot_scale=self.rot_scale)
+                           self.rot_dims, self.eps, ctx.status, rot_scale=self.rot_scale,
+                           freq_lo=self.freq_lo)
         gate = self.input.view(proj, "gate") if self.head_gate else None
         width = self.rank + self.rot_dim
         if self.tensor_cores:
@@ -358,7 +360,7 @@ class LatentAttention(Mixer):
             q = self.input.view(proj, "q")
         qa = ctx.scratch("latent_qa", (cap, self.heads, width), torch.float32)[:t]
         ops.latent_fold(qa, q, self.uk, ctx.positions, self.freq, self.heads, self.dim,
-                        self.rot_dim, self.rot_dims, self.rank)
+                        self.rot_dim, self.rot_dims, self.rank, freq_lo=self.freq_lo)
         lat = ctx.scratch("latent_sum", (cap, self.heads, self.rank), torch.float32)[:t]
         attend_latent(ctx, lat, qa, cache, group, self.sinks, self.scale, self.window, self.rank)
         o = ctx.scratch_zero("latent_o", (cap, self.out.n_in), dtype)[:t]

@@ -6,24 +6,39 @@ from __future__ import annotations
 import torch
 
 
-def rotary_frequencies(base: float, dims: int, device, divide_by: float = 1.0) -> torch.Tensor:
+def rotary_frequencies(base: float, dims: int, device, divide_by: float = 1.0,
+                       with_lo: bool = False):
     """float32 [max(1, dims / 2)] (a table of one zero when nothing is rotated); ``divide_by``:
-    linear scaling of the positions, every frequency divided by it."""
+    linear scaling of the positions, every frequency divided by it.  ``with_lo``: (hi, lo)
+    tables, see :func:`split_frequencies`."""
     if dims < 0 or dims % 2:
         raise ValueError(f"rotary positions need an even number of coordinates, got {dims}")
     half = dims // 2
     freq = [float(base) ** (-2.0 * i / dims) / float(divide_by) for i in range(half)] or [0.0]
+    if with_lo:
+        return split_frequencies(freq, device)
     return torch.tensor(freq, dtype=torch.float64).to(torch.float32).to(device)
 
 
+def split_frequencies(freq64, device):
+    """(hi, lo) float32 tables of frequencies given in 64-bit: hi is the rounded frequency, lo
+    what the rounding left out.  The kernels that take ``freq_lo`` add the two in 64-bit, so the
+    angle position x frequency keeps the frequency's full precision."""
+    f64 = torch.as_tensor(freq64, dtype=torch.float64)
+    hi = f64.to(torch.float32)
+    lo = (f64 - hi.to(torch.float64)).to(torch.float32)
+    return hi.to(device), lo.to(device)
+
+
 def yarn_frequencies(base: float, dims: int, factor: float, original: float, fast: float,
-                     slow: float, device):
+                     slow: float, device, with_lo: bool = False):
     """(frequencies float32 [dims / 2], magnitude) of YaRN-scaled rotary positions.  With
     d(t) = dims * ln(original / (2 pi t)) / (2 ln base), lo = max(floor(d(fast)), 0), hi =
     min(ceil(d(slow)), dims - 1) and ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1),
     frequency i is f_i / factor * ramp_i + f_i * (1 - ramp_i) (fast-turning pairs keep their
     frequency, slow ones are interpolated), and cos and sin are both multiplied by the
-    magnitude 0.1 * ln(factor) + 1."""
+    magnitude 0.1 * ln(factor) + 1.  ``with_lo``: the frequencies as (hi, lo) tables, see
+    :func:`split_frequencies`."""
     import math
     if dims <= 0 or dims % 2:
         raise ValueError(f"rotary positions need an even number of coordinates, got {dims}")
@@ -39,4 +54,6 @@ def yarn_frequencies(base: float, dims: int, factor: float, original: float, fas
         ramp = min(max((i - lo) / max(hi - lo, 0.001), 0.0), 1.0)
         freq.append(f / factor * ramp + f * (1.0 - ramp))
     table = torch.tensor(freq, dtype=torch.float64).to(torch.float32).to(device)
+    if with_lo:
+        return split_frequencies(freq, device), 0.1 * math.log(factor) + 1.0
     return table, 0.1 * math.log(factor) + 1.0

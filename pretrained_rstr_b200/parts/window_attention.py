@@ -116,8 +116,9 @@ class WindowAttention(Mixer):
             self.slopes = torch.tensor([2.0 ** (-bits * (h + 1) / self.heads)
                                         for h in range(self.heads)],
                                        dtype=torch.float64).to(torch.float32).to(dev)
-        self.freq = rotary_frequencies(float(p.get("rot_base", 10000.0)), self.rot_dims, dev,
-                                       divide_by=float(p.get("rot_factor") or 1.0))
+        self.freq, self.freq_lo = rotary_frequencies(
+            float(p.get("rot_base", 10000.0)), self.rot_dims, dev,
+            divide_by=float(p.get("rot_factor") or 1.0), with_lo=True)
         gpu = torch.cuda.is_available()
         self.tile_rows = ops.wattn_tile_rows(self.heads, self.kv_heads, self.dim, self.vdim) if gpu else 0
         self.single_ok = gpu and ops.wattn_single_supports(self.heads, self.kv_heads, self.dim, self.vdim)
@@ -157,7 +158,7 @@ class WindowAttention(Mixer):
                           None if self.shares_cache else group.slots, ctx.positions, self.freq,
                           self.heads, self.kv_heads, self.dim, self.vdim, self.rot_dims, self.eps,
                           self.temp_coef, self.temp_every, ctx.status, head_norm=self.head_norm,
-                          biases=self.biases)
+                          biases=self.biases, freq_lo=self.freq_lo)
         o = ctx.scratch_zero("wattn_out", (cap, self.out.n_in), self.runtime.dtype)[:t]
         # a step of single tokens: a CTA per (token, key/value head) whose warps share out the
         # key blocks (rows of different requests share no keys); sizes that kernel does not
