@@ -1828,8 +1828,8 @@ def lru_conv(u, proj, x_col: int, x_bias, conv_w, conv_b, conv_state, seq_of_tok
 
 def lru_gates(a_out, u, wa_t, wi_t, ba, bi, decay, blocks: int) -> None:
     """Per token and block b of the channels: r = sigmoid(A_b u_b + ba), i = sigmoid(B_b u_b +
-    bi) (``wa_t`` / ``wi_t``: [blocks, in, out], the block matrices transposed), log a = decay * r
-    to ``a_out`` and sqrt(1 - a^2) * i * u in place of u; 32-bit arithmetic."""
+    bi) (``wa_t`` / ``wi_t``: [blocks, in, out], the block matrices transposed), a - 1 = expm1(decay
+    * r) to ``a_out`` and sqrt(1 - a^2) * i * u in place of u; 32-bit arithmetic."""
     what = "lru_gates"
     _need(a_out, torch.float32, "a_out", what)
     _need(u, torch.float32, "u", what)
@@ -1901,9 +1901,8 @@ def lru_step(out, proj, y_col: int, x_col: int, y_bias, x_bias, conv_w, conv_b, 
 def lru_scan(out, a_in, inp, proj, y_col: int, x_col: int, y_bias, x_bias, state, conv_state,
              q_start, state_slot, positions, n_requests: int, out_scale: float = 1.0,
              segments=None) -> None:
-    """S_t = a_t S_(t-1) + inp_t per (request, channel), with ``a_in`` holding log a_t (the
-    step is taken as S + (inp - (1 - a) S) with 1 - a = -expm1(log a), which keeps a decay
-    close to one exact), from and to ``state`` [slots, width] (zero at position 0); out[t, c] = S_t * gelu_tanh(proj[t, y_col + c] + y_bias[c]) *
+    """S_t = a_t S_(t-1) + inp_t per (request, channel), with ``a_in`` holding a_t - 1 (the
+    step is taken as S + (inp + (a - 1) S), which keeps a decay close to one exact), from and to ``state`` [slots, width] (zero at position 0); out[t, c] = S_t * gelu_tanh(proj[t, y_col + c] + y_bias[c]) *
     out_scale; ``conv_state`` then holds the request's last taps - 1 inputs proj[:, x_col + c] +
     x_bias[c].  ``segments`` = (own, keep), two float32 workspaces [n, width] for n >=
     lru_max_segments: portions run in segments of 64 tokens side by side (two launches)."""

@@ -7,10 +7,12 @@
 //       i_t = sigmoid(B_b u_t,b + b_b)
 //       log a_t = decay_c * r_t              decay_c = -const * softplus(lambda_c), given
 //       S_t = a_t S_(t-1) + sqrt(1 - a_t^2) * i_t * u_t          (S_(-1) = 0)
+//     (a_t travels as a_t - 1 = expm1(log a_t), 1 - a_t^2 is -(a_t - 1)(a_t + 1): both keep their
+//     precision when a_t is close to one)
 //       out_t = S_t * gelu_tanh(y_t)
 //     lru_conv (a CTA per token; the taps before a portion's first token come from the
 //     request's saved inputs), lru_gates (a CTA per (8 tokens, block): the two block matrices
-//     in 32-bit FMA, log a_t and the recurrence's input), lru_scan (a thread per (request,
+//     in 32-bit FMA, a_t - 1 and the recurrence's input), lru_scan (a thread per (request,
 //     channel) walks the request's tokens in order from and to the state slot, multiplies by
 //     the other branch and brings the saved inputs up to date).
 //
@@ -32,12 +34,13 @@ namespace {
 __device__ __forceinline__ float ru_sigmoid(float z) { return 1.0f / (1.0f + expf(-z)); }
 __device__ __forceinline__ float ru_logsigmoid(float z) { return fminf(z, 0.0f) - log1pf(expf(-fabsf(z))); }
 
-// One step of S <- a S + input, given log a.  A decay close to one, rounded to 32 bits, is off
+// One step of S <- a S + input, given a - 1.  A decay close to one, rounded to 32 bits, is off
 // by up to 3e-8, which is a relative error of 3e-8 / (1 - a) in how fast the state fades: over
-// a thousand tokens at a = 0.999 a far token's weight would be off by 3e-5.  1 - a = -expm1(log
-// a) keeps its full relative precision, so the step is taken as S + (input - (1 - a) S).
-__device__ __forceinline__ float lru_decay(float s, float log_a, float input) {
-    return s + fmaf(expm1f(log_a), s, input);
+// a thousand tokens at a = 0.999 a far token's weight would be off by 3e-5.  a - 1 = expm1(log
+// a) keeps its full relative precision, so the decay travels as a - 1 and the step is taken as
+// S + (input + (a - 1) S).
+__device__ __forceinline__ float lru_decay(float s, float a_minus_1, float input) {
+    return s + fmaf(a_minus_1, s, input);
 }
 
 // ------------------------------------------------------------------ (1) convolution
@@ -81,7 +84,7 @@ __global__ void lru_conv_kernel(float* __restrict__ u, const float* __restrict__
 
 // ------------------------------------------------------------------------ (1) gates
 constexpr int LRU_TOK = 8;
-// wa_t, wi_t: [blocks, bw (in), bw (out)]; a_out[t, c] = log a_t; u[t, c] <- sqrt(1 - a^2) * i * u.
+// wa_t, wi_t: [blocks, bw (in), bw (out)]; a_out[t, c] = a_t - 1; u[t, c] <- sqrt(1 - a^2) * i * u.
 template <typename W>
 __global__ void __launch_bounds__(128)
 lru_gates_kernel(float* __restrict__ a_out, float* __restrict__ u, const W* __restrict__ wa_t,
@@ -120,9 +123,9 @@ lru_gates_kernel(float* __restrict__ a_out, float* __restrict__ u, const W* __re
         for (int k = 0; k < LRU_TOK; ++k) {
             if (k >= nt) break;
             const float r = ru_sigmoid(ra[k] + bac), g = ru_sigmoid(ri[k] + bic);
-            const float la = dc * r;                             // log a <= 0
-            const float in = sqrtf(fmaxf(-expm1f(2.0f * la), 0.0f)) * g * us[k * bw + o];
-            a_out[(size_t)(t0 + k) * width + c] = la;            // (the logarithm: see lru_decay)
+            const float am1 = expm1f(dc * r);                    // a - 1 (log a = dc r <= 0); see lru_decay
+            const float in = sqrtf(fmaxf(-am1 * (am1 + 2.0f), 0.0f)) * g * us[k * bw + o];   // 1 - a^2 = -(a - 1)(a + 1)
+            a_out[(size_t)(t0 + k) * width + c] = am1;
             u[(size_t)(t0 + k) * width + c] = in;
         }
     }
@@ -262,9 +265,9 @@ __global__ void lru_step_kernel(LruStepArgs g) {
         for (int k = 0; k < LRU_TOK; ++k) {
             if (k >= nt) break;
             const float r = ru_sigmoid(ra[k] + bac), gi = ru_sigmoid(ri[k] + bic);
-            const float la = dc * r;
-            const float in = sqrtf(fmaxf(-expm1f(2.0f * la), 0.0f)) * gi * us[k * bw + o];
-            s = lru_decay(s, la, in);
+            const float am1 = expm1f(dc * r);                    // a - 1; 1 - a^2 = -(a - 1)(a + 1)
+            const float in = sqrtf(fmaxf(-am1 * (am1 + 2.0f), 0.0f)) * gi * us[k * bw + o];
+            s = lru_decay(s, am1, in);
             const float y = prb_activate(g.proj[(size_t)(tb + k) * g.ld + g.y_col + c] + yb, PRB_ACT_GELU_TANH);
             out[(size_t)(tb + k) * g.out_ld + c] = prb_from_float<O>(s * y * g.out_scale);
         }
@@ -297,7 +300,7 @@ __global__ void lru_step_kernel(LruStepArgs g) {
 // ------------------------------------------------- (1) long portions: the scan in segments
 // Segment z of the launch is segment s of request b (numbered in request order).  Pass 1: a
 // thread per (segment, channel) builds, from zero, what the segment's own tokens leave and the
-// logarithm of the product of its decays.  Pass 2: a thread per (segment, channel) first walks the request's
+// product of its decays minus one.  Pass 2: a thread per (segment, channel) first walks the request's
 // earlier segments, U <- product U + own from the carried state, then runs its own tokens with
 // outputs; a request's last segment leaves the state and the saved inputs in the slot.
 constexpr int LRU_SEG = 64;
@@ -326,12 +329,12 @@ lru_seg_own_kernel(float* __restrict__ seg_own, float* __restrict__ seg_keep,
     const int c = blockIdx.y * blockDim.x + threadIdx.x;
     if (c >= width || s == nseg - 1) return;         // (a last segment's own sum is never needed)
     const int t0 = q_start[b] + s * LRU_SEG, t1 = min(min(q_start[b + 1], n_tokens), t0 + LRU_SEG);
-    float own = 0.0f, keep = 0.0f;                   // (keep: the LOGARITHM of the decays' product)
+    float own = 0.0f, keep = 0.0f;                   // (keep: the decays' product MINUS ONE)
 #pragma unroll 8
     for (int r = t0; r < t1; ++r) {
-        const float la = a_in[(size_t)r * width + c];
-        own = lru_decay(own, la, in[(size_t)r * width + c]);
-        keep += la;
+        const float am1 = a_in[(size_t)r * width + c];
+        own = lru_decay(own, am1, in[(size_t)r * width + c]);
+        keep = fmaf(keep, am1, keep + am1);          // (1 + keep)(1 + am1) - 1
     }
     seg_own[(size_t)blockIdx.x * width + c] = own;
     seg_keep[(size_t)blockIdx.x * width + c] = keep;

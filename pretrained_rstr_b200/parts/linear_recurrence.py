@@ -18,9 +18,9 @@ prompt may be cut anywhere and decoding is the same kernels with one token.  Ste
 tokens are one launch (a CTA per (request, block)); longer portions run the convolution, the
 gates and then the recurrence in segments of 64 tokens side by side.  Wy and Wx are
 one product whose 32-bit result feeds everything after it unrounded; the block matrices, the
-gates, the decays, the recurrence and the state are 32-bit; a decay travels as its logarithm
-and a step is S + (input - (1 - a) S) with 1 - a = -expm1(log a), so that a decay close to
-one keeps its precision.  Sizes, taps, blocks, the decay's
+gates, the decays, the recurrence and the state are 32-bit; a decay travels as a - 1 =
+expm1(log a) and a step is S + (input + (a - 1) S), so that a decay close to one keeps its
+precision.  Sizes, taps, blocks, the decay's
 constant and the constant on the result are parameters.
 """
 from __future__ import annotations
