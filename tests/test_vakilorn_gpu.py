@@ -622,6 +622,43 @@ def test_whole_prompts_decode_and_portions(folders, name, dtype):
     compare(rp.rows, oracle, TOL[dtype])
 
 
+def test_sizes_beyond_the_one_launch_kernels(tmp_path):
+    """A memory head whose state does not fit a CTA's shared memory (every step takes the scan),
+    a recurrence of one block and one of blocks of a single channel, a convolution of seven
+    taps, attention heads of odd sizes: prompts whole, then cut with the last tokens one by one."""
+    from pretrained_rstr_b200.config.registry import lookup
+    from pretrained_rstr_b200.weights import make_random_model
+    raw = _model(211, 128, [
+        _mem(_left(4, 1, 64, 136, rot_dims=64, factor=3.0), 1, 256, 256, 9.0, _dense(64, 2.0)),
+        _rec(_left(8, 2, 32, 32), 384, 1, 2, _dense(64, 2.0)),
+        _rec(_left(2, 2, 130, 34, rot_dims=2), 48, 48, 7, None)], 257, 9, 4, 11.0)
+    cfg = lookup(raw).config_class.from_dict(raw)
+    folder = str(tmp_path / "model")
+    make_random_model(folder, cfg, 5, torch.float32)
+    c, W = P.read_folder(folder)
+    prompts = {f"r{i}": random_tokens(n, raw["vocab"], 70 + i) for i, n in enumerate([3, 90, 200])}
+    oracle = {rid: P.forward(ids, W, c).to(torch.float32) for rid, ids in prompts.items()}
+    rp = Replayer(folder, "float32", max_tokens=512)
+    for rid, ids in prompts.items():
+        rp.step([(rid, ids, list(range(len(ids))))], end=[rid])
+    compare(rp.rows, oracle, TOL["float32"])
+    rp.rows.clear()
+    for rid, ids in prompts.items():
+        head = max(1, len(ids) - 20)
+        at = 0
+        for n in (2, 70, 1, 64, 500):
+            n = min(n, head - at)
+            if n > 0:
+                rp.step([(rid, ids[at:at + n], list(range(n)))])
+                at += n
+        for i in range(head, len(ids)):
+            rp.step([(rid, ids[i:i + 1], [0])], end=[rid] if i == len(ids) - 1 else [])
+        if head == len(ids):
+            rp.lm.cache.close(rid)
+            del rp.pos[rid]
+    compare(rp.rows, oracle, TOL["float32"])
+
+
 @pytest.mark.parametrize("name,dtype", [("A", "float32"), ("B", "bfloat16"), ("B", "float32"), ("C", "float32")])
 def test_long_decode(folders, name, dtype):
     """Two tokens of prompt and some 340 decoded one by one: every window and several pages'
